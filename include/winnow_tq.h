@@ -1,0 +1,143 @@
+/*
+ * winnow_tq.h - C ABI of libwinnow_tq.so: the sm_100a CUDA backend for the
+ * TurboQuant packed-KV decode path of lgoyal6/winnow (turboquant_kv/).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its comment says "host";
+ *   - buffers are borrowed for the duration of the call's work on `stream`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); calls only enqueue work, they never synchronise;
+ *   - return value: WTQ_OK or a negative WTQ_ERR_* code, with a text in
+ *     wtq_last_error() (thread-local).  Nothing throws or aborts.  Argument
+ *     errors are reported before anything is launched;
+ *   - `status` (optional, may be NULL) is a device int32 the kernels OR bits
+ *     into when they meet data they refuse to follow (a page id outside the
+ *     pool, a position outside the page table); such accesses are skipped,
+ *     never performed.  The caller zeroes it and reads it when it likes;
+ *   - dtype codes: WTQ_F32 / WTQ_F16 / WTQ_BF16.
+ *
+ * Layouts (reference: turboquant_kv/packed_attention.py:20-29,
+ * turboquant_kv/page_pool.py:63-86)
+ *   pages      (P, Hkv, S, NB) uint8, NB = D*bw/8, rows of NB bytes contiguous,
+ *              S rows contiguous; page and head strides given in BYTES
+ *   norms      (P, Hkv, S) fp16, S contiguous; strides given in ELEMENTS
+ *   page_table (B, max_pages) int32, unused slots -1; row stride in elements
+ *   seq_lens   (B,) int32, tokens stored per sequence (including this step's)
+ *   codes      LSB-first bit stream per row (turboquant_kv/packing.py:14-18)
+ */
+#ifndef WINNOW_TQ_H_
+#define WINNOW_TQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WTQ_OK 0
+#define WTQ_ERR_ARG (-1)         /* malformed argument (shape, stride, null) */
+#define WTQ_ERR_UNSUPPORTED (-2) /* legal request this build has no kernel for */
+#define WTQ_ERR_CUDA (-3)        /* a CUDA runtime call failed */
+#define WTQ_ERR_WORKSPACE (-4)   /* workspace too small */
+
+#define WTQ_F32 0
+#define WTQ_F16 1
+#define WTQ_BF16 2
+
+/* status bits written by kernels */
+#define WTQ_STATUS_BAD_PAGE 1     /* page id outside [0, P) was skipped */
+#define WTQ_STATUS_BAD_POSITION 2 /* token position outside the page table */
+
+/* order of the fp32 summation in the rotation of wtq_quantize / wtq_append.
+ * The reference computes (x/|x|) @ Pi^T with a CPU BLAS whose order depends
+ * on the number of vectors in the call (turboquant_kv/cache.py:108-115);
+ * WTQ_ORDER_AUTO picks the order that BLAS uses for `rows` vectors. */
+#define WTQ_ORDER_AUTO (-1)
+#define WTQ_ORDER_SEQUENTIAL 0
+#define WTQ_ORDER_INTERLEAVED16 1
+
+/* Library version (major*10000 + minor*100 + patch) and last error text. */
+int wtq_version(void);
+const char *wtq_last_error(void);
+
+/* Replaces packing.pack (turboquant_kv/packing.py:38-64).
+ * idx (rows, D) uint8 contiguous -> out (rows, D*bw/8) uint8 contiguous. */
+int wtq_pack(const uint8_t *idx, uint8_t *out, int64_t rows, int D, int bw, void *stream);
+
+/* Replaces packing.unpack (turboquant_kv/packing.py:68-89). */
+int wtq_unpack(const uint8_t *packed, uint8_t *idx, int64_t rows, int D, int bw, void *stream);
+
+/* Replaces TurboQuantMSE.quantize (turboquant_kv/cache.py:108-115), optionally
+ * fused with packing.pack.  x: `rows` vectors of D elements of `dtype`,
+ * vector r at x + r*row_stride (elements), contiguous inside a vector.
+ * Pi (D, D) fp32 row-major; bounds (2^bw - 1) fp32 ascending.
+ * Outputs, each optional (NULL to skip): idx (rows, D) uint8; packed
+ * (rows, D*bw/8) uint8; norms (rows) fp32 (clamped at 1e-10, as returned by
+ * the reference). */
+int wtq_quantize(const void *x, int dtype, int64_t rows, int64_t row_stride, int D,
+                 const float *Pi, const float *bounds, int bw, int order, uint8_t *idx,
+                 uint8_t *packed, float *norms, void *stream);
+
+/* Replaces the packed branch of PagedPackedCache.update
+ * (turboquant_kv/packed_backend.py:135-170): rotate, take the norm, quantize,
+ * bit-pack and scatter n new tokens per sequence into one layer's pages, for K
+ * and V, in one launch.  k, v: (B, Hkv, n, D) of `dtype` with element strides
+ * {batch, head, token} (the last dimension is contiguous).  Token i of
+ * sequence b lands at position seq_lens[b] - n + i, i.e. in page
+ * page_table[b][pos / S], slot pos % S.  Norms are stored as fp16 (round to
+ * nearest even).  `order` as in wtq_quantize, with rows = B*Hkv*n. */
+typedef struct {
+  uint8_t *pages;        /* one layer: (P, Hkv, S, NB) */
+  void *norms;           /* fp16 (P, Hkv, S) */
+  int64_t page_stride;   /* bytes between pages */
+  int64_t head_stride;   /* bytes between kv heads */
+  int64_t norm_page_stride; /* elements */
+  int64_t norm_head_stride; /* elements */
+  const float *Pi;       /* (D, D) */
+  const float *bounds;   /* 2^bw - 1 (append) */
+  const float *centroids;/* 2^bw     (decode) */
+  int bw;
+} wtq_side_t;
+
+int wtq_append(const void *k, const void *v, int dtype, const int64_t k_strides[3],
+               const int64_t v_strides[3], const wtq_side_t *k_side, const wtq_side_t *v_side,
+               const int32_t *page_table, int64_t table_stride, const int32_t *seq_lens, int B,
+               int Hkv, int n, int D, int S, int P, int max_pages, int order, int32_t *status,
+               void *stream);
+
+/* Replaces packed_decode_attention (turboquant_kv/packed_attention_triton.py:
+ * 180-187, 204-262): one query token per sequence attends to its packed
+ * history.  q: (B, Hq, D) of `dtype`, element strides {batch, head}; out:
+ * same shape, own strides, same dtype (it may be a slice of a larger gathered
+ * buffer).  Query head h reads kv head h / (Hq/Hkv).  num_splits <= 0 lets the
+ * library choose.  The rotated query, the split-K partial states and the merge
+ * live in `workspace` (wtq_decode_workspace_bytes); nothing else is allocated.
+ * The first wtq_decode_counter_bytes() of the workspace must be zero on entry
+ * and are zero again when the call's work completes.  Sequences of length 0
+ * produce exact zeros. */
+size_t wtq_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_pages, int S,
+                                  int num_splits);
+size_t wtq_decode_counter_bytes(int B, int Hkv);
+int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pages, int S, int bw_k,
+                           int bw_v);
+int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], void *out,
+               const int64_t out_strides[2], const wtq_side_t *k_side, const wtq_side_t *v_side,
+               const int32_t *page_table, int64_t table_stride, const int32_t *seq_lens,
+               float scale, int B, int Hq, int Hkv, int D, int S, int P, int max_pages,
+               int num_splits, void *workspace, size_t workspace_bytes, int32_t *status,
+               void *stream);
+
+/* Replaces tq_dequant / tq_dequant_cuda (turboquant_kv/kernel.py:78-115,
+ * turboquant_kv/csrc/tq_dequant.cu:186-211): N packed rows -> (N, D) of
+ * `out_dtype`.  Logical row r is read from source row (r / L) * MAXLEN + r % L
+ * (a (planes, MAXLEN, NB) buffer viewed through its first L positions);
+ * out[r] = (centroids[codes] @ Pi) * norm. */
+int wtq_dequant(const uint8_t *packed, const void *norms_f16, const float *centroids,
+                const float *Pi, void *out, int out_dtype, int bw, int D, int64_t N, int64_t L,
+                int64_t MAXLEN, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WINNOW_TQ_H_ */

@@ -1,0 +1,106 @@
+"""ctypes binding of libwinnow_tq.so.  There is no fallback: if the library is
+absent or a call fails, the caller gets an exception."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+import torch
+
+from ._build import LIB
+
+WTQ_F32, WTQ_F16, WTQ_BF16 = 0, 1, 2
+ORDER_AUTO, ORDER_SEQUENTIAL, ORDER_INTERLEAVED16 = -1, 0, 1
+STATUS_BAD_PAGE, STATUS_BAD_POSITION = 1, 2
+
+_DTYPES = {torch.float32: WTQ_F32, torch.float16: WTQ_F16, torch.bfloat16: WTQ_BF16}
+
+
+class BackendError(RuntimeError):
+    """The CUDA library is missing, or one of its entry points refused a call."""
+
+
+class Side(ctypes.Structure):
+    """Mirror of wtq_side_t (include/winnow_tq.h)."""
+    _fields_ = [("pages", c_void_p), ("norms", c_void_p),
+                ("page_stride", c_int64), ("head_stride", c_int64),
+                ("norm_page_stride", c_int64), ("norm_head_stride", c_int64),
+                ("Pi", c_void_p), ("bounds", c_void_p), ("centroids", c_void_p),
+                ("bw", c_int)]
+
+
+_SIGNATURES = {
+    "wtq_version": (c_int, []),
+    "wtq_last_error": (ctypes.c_char_p, []),
+    "wtq_pack": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "wtq_unpack": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "wtq_quantize": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int,
+                             c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "wtq_append": (c_int, [c_void_p, c_void_p, c_int, ctypes.POINTER(c_int64),
+                           ctypes.POINTER(c_int64), ctypes.POINTER(Side), ctypes.POINTER(Side),
+                           c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_void_p, c_void_p]),
+    "wtq_decode_workspace_bytes": (c_size_t, [c_int] * 7),
+    "wtq_decode_counter_bytes": (c_size_t, [c_int, c_int]),
+    "wtq_decode_auto_splits": (c_int, [c_int] * 8),
+    "wtq_decode": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p,
+                           ctypes.POINTER(c_int64), ctypes.POINTER(Side), ctypes.POINTER(Side),
+                           c_void_p, c_int64, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "wtq_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_int64, c_int64, c_int64, c_void_p]),
+}
+
+_lib = None
+
+
+def exported_symbols() -> list[str]:
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not LIB.exists():
+            raise BackendError(
+                f"{LIB} is not built; run `python -c \"import __graft_entry__ as g; g.build()\"` "
+                "(needs nvcc). This package has no CPU or library fallback.")
+        handle = ctypes.CDLL(str(LIB))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)     # AttributeError if the symbol is missing
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise BackendError(f"libwinnow_tq error {rc}: {lib().wtq_last_error().decode()}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise BackendError(f"dtype {dtype} is not supported (float32, float16, bfloat16)") from None
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if not t.is_cuda:
+            raise BackendError(
+                "the winnow_b200 operators run on CUDA tensors only; there is no CPU path")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise BackendError(f"operands on different devices: {dev} and {t.device}")
+    return dev
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def i64x(*values: int):
+    return (c_int64 * len(values))(*values)

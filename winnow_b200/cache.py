@@ -1,0 +1,167 @@
+"""TurboQuant quantizer: fixed random rotation + Lloyd-Max scalar codebook.
+
+Construction (rotation by QR of a CPU-seeded Gaussian matrix, codebook by
+Lloyd-Max iteration in float64) runs once per (bit width, head_dim, seed) on the
+host and defines the codebook bit for bit, as in the reference
+(turboquant_kv/cache.py:62-106,134-148).  `quantize` and `dequantize_into` run
+on the GPU through libwinnow_tq.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from .packing import packed_bytes
+
+
+def _lloyd_max_gaussian(levels: int, sigma: float = 1.0, iters: int = 200, tol: float = 1e-12):
+    """Lloyd-Max centroids and bucket edges (with the +-inf ends) for
+    N(0, sigma^2), float64.  Evenly spaced start on [-3 sigma, 3 sigma]; edges
+    midway between neighbours; centroids to the conditional mean of their bucket;
+    stop when no centroid moves more than `tol`."""
+    from scipy.stats import norm
+
+    c = np.linspace(-3.0 * sigma, 3.0 * sigma, levels)
+    for _ in range(iters):
+        z = np.concatenate(([-np.inf], 0.5 * (c[:-1] + c[1:]), [np.inf])) / sigma
+        mass = norm.cdf(z[1:]) - norm.cdf(z[:-1])
+        first_moment = sigma * (norm.pdf(z[:-1]) - norm.pdf(z[1:]))
+        with np.errstate(divide="ignore", invalid="ignore"):
+            nxt = np.where(mass < 1e-300, c, first_moment / mass)
+        converged = np.max(np.abs(nxt - c)) < tol
+        c = nxt
+        if converged:
+            break
+    return c, np.concatenate(([-np.inf], 0.5 * (c[:-1] + c[1:]), [np.inf]))
+
+
+class TurboQuantMSE:
+    """Pi (D, D) fp32, centroids (2^bw) fp32, boundaries (2^bw - 1) fp32."""
+
+    def __init__(self, bit_width: int, head_dim: int, device="cpu", rotation_seed: int = 42):
+        packed_bytes(head_dim, bit_width)
+        device = torch.device(device)
+        gen = torch.Generator(device="cpu").manual_seed(rotation_seed)
+        gauss = torch.randn(head_dim, head_dim, generator=gen, dtype=torch.float32)
+        Q, R = torch.linalg.qr(gauss)
+        signs = torch.sign(torch.diag(R))
+        signs[signs == 0] = 1.0
+        self.Pi = (Q * signs.unsqueeze(0)).to(device).contiguous()
+        c, edges = _lloyd_max_gaussian(2 ** bit_width, sigma=1.0 / math.sqrt(head_dim))
+        self.centroids = torch.tensor(c, dtype=torch.float32, device=device).contiguous()
+        self.boundaries = torch.tensor(edges[1:-1], dtype=torch.float32, device=device).contiguous()
+        self.bit_width, self.head_dim, self.device = bit_width, head_dim, device
+
+    @torch.no_grad()
+    def quantize(self, x: torch.Tensor, *, order: int = _lib.ORDER_AUTO, packed: bool = False):
+        """(..., D) -> (uint8 idx (..., D), fp32 norms (...,)).
+
+        With `packed=True` the first result is the bit-packed rows
+        (..., D*bw/8) instead, produced by the same launch.  `order` selects the
+        summation order of the rotation (see include/winnow_tq.h); the default
+        follows the reference's CPU arithmetic for this many vectors.
+        """
+        D = self.head_dim
+        if x.shape[-1] != D:
+            raise ValueError(f"last dimension {x.shape[-1]} != head_dim {D}")
+        dev = _lib.require_cuda(x, self.Pi)
+        src = x if x.dtype in (torch.float32, torch.float16, torch.bfloat16) else x.float()
+        src = src.reshape(-1, D)
+        if src.stride(-1) != 1:
+            src = src.contiguous()
+        rows = src.shape[0]
+        nb = packed_bytes(D, self.bit_width)
+        codes = torch.empty(*x.shape[:-1], nb if packed else D, dtype=torch.uint8, device=dev)
+        norms = torch.empty(x.shape[:-1], dtype=torch.float32, device=dev)
+        if rows:
+            with torch.cuda.device(dev):
+                _lib.check(_lib.lib().wtq_quantize(
+                    src.data_ptr(), _lib.dtype_code(src.dtype), rows, src.stride(0), D,
+                    self.Pi.data_ptr(), self.boundaries.data_ptr(), self.bit_width, order,
+                    None if packed else codes.data_ptr(), codes.data_ptr() if packed else None,
+                    norms.data_ptr(), _lib.stream_ptr(dev)))
+        return codes, norms
+
+    @torch.no_grad()
+    def dequantize_into(self, idx: torch.Tensor, norms: torch.Tensor, out: torch.Tensor) -> None:
+        """Reconstruct `centroids[idx] @ Pi * norms` into `out` (fp32/fp16/bf16)."""
+        from .packing import pack
+        rows = pack(idx.reshape(-1, self.head_dim), self.bit_width)
+        dequantize_rows(rows, norms.reshape(-1).to(torch.float16), self.centroids, self.Pi,
+                        self.bit_width, self.head_dim, out=out)
+
+
+@torch.no_grad()
+def dequantize_rows(packed: torch.Tensor, norms: torch.Tensor, centroids: torch.Tensor,
+                    Pi: torch.Tensor, bit_width: int, head_dim: int,
+                    out: torch.Tensor | None = None, allow_tf32: bool = False) -> torch.Tensor:
+    """Fused dequantisation of packed rows, the counterpart of the reference's
+    `tq_dequant` (turboquant_kv/kernel.py:78-115).
+
+    `packed` is (..., NB) uint8 and `norms` (...,) fp16.  A (B, H, L, NB) slice
+    of a (B, H, MAXLEN, NB) buffer is read in place through its strides.
+    Returns (..., head_dim) in `out`'s dtype (bf16 when `out` is None).
+    """
+    del allow_tf32                      # the CUDA backend always computes in fp32
+    dev = _lib.require_cuda(packed, norms, centroids, Pi)
+    nb = packed_bytes(head_dim, bit_width)
+    if packed.dtype != torch.uint8 or packed.shape[-1] != nb:
+        raise ValueError(f"packed rows must be uint8 with {nb} bytes")
+    if norms.dtype != torch.float16:
+        raise ValueError("norms must be fp16")
+    lead = packed.shape[:-1]
+    N = 1
+    for s in lead:
+        N *= s
+    L = lead[-1] if lead else 1
+    maxlen = L
+    src, nsrc = packed, norms
+    if (packed.dim() >= 3 and not packed.is_contiguous() and _is_plane_slice(packed, nb)
+            and _is_plane_slice(norms.unsqueeze(-1), 1)
+            and norms.stride(-2) * nb == packed.stride(-3)):
+        maxlen = packed.stride(-3) // nb
+    elif not packed.is_contiguous() or not norms.is_contiguous():
+        src, nsrc = packed.contiguous(), norms.contiguous()
+    if out is None:
+        out = torch.empty(*lead, head_dim, dtype=torch.bfloat16, device=dev)
+    if not out.is_contiguous() or out.numel() != N * head_dim:
+        raise ValueError("out must be contiguous with shape (..., head_dim)")
+    if N:
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().wtq_dequant(
+                src.data_ptr(), nsrc.data_ptr(), centroids.data_ptr(), Pi.data_ptr(),
+                out.data_ptr(), _lib.dtype_code(out.dtype), bit_width, head_dim, N, L, maxlen,
+                _lib.stream_ptr(dev)))
+    return out
+
+
+def _is_plane_slice(t: torch.Tensor, row: int) -> bool:
+    """True when `t` (..., L, row) is the first-L-positions view of a dense
+    (..., MAXLEN, row) buffer: the leading dimensions are contiguous over planes
+    of MAXLEN rows."""
+    if t.stride(-1) != 1 or t.stride(-2) != row:
+        return False
+    plane = t.stride(-3)
+    if plane % row or plane < t.shape[-2] * row:
+        return False
+    expect = plane
+    for size, stride in zip(reversed(t.shape[:-2]), reversed(t.stride()[:-2])):
+        if size != 1 and stride != expect:
+            return False
+        expect *= size
+    return True
+
+
+_QUANTIZER_CACHE: dict = {}
+
+
+def _get_quantizer(bw, dim, dev, seed=42) -> TurboQuantMSE:
+    """One quantizer per (bit width, head_dim, device, seed); building one costs
+    a scipy iteration, and every layer of a model shares it."""
+    key = (bw, dim, str(dev), seed)
+    if key not in _QUANTIZER_CACHE:
+        _QUANTIZER_CACHE[key] = TurboQuantMSE(bw, dim, dev, rotation_seed=seed)
+    return _QUANTIZER_CACHE[key]

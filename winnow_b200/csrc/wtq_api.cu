@@ -1,0 +1,132 @@
+// Host entry points of wtq_decode: argument checks, workspace carving, launch
+// order.  Nothing here allocates or synchronises.
+#include "wtq_decode.cuh"
+
+using namespace wtq;
+
+namespace {
+
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int device_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  return sms;
+}
+
+int clamp_splits(int splits, int max_pages, int S) {
+  const int64_t tokens = (int64_t)max_pages * S;
+  int64_t tiles = (tokens + 127) / 128;
+  if (tiles < 1) tiles = 1;
+  if (splits > tiles) splits = (int)tiles;
+  if (splits > kMaxSplits) splits = kMaxSplits;
+  if (splits < 1) splits = 1;
+  return splits;
+}
+
+bool fill_side(DecodeSideDev &d, const wtq_side_t &w, int D) {
+  d.pages = w.pages;
+  d.norms = (const __half *)w.norms;
+  d.page_stride = w.page_stride;
+  d.head_stride = w.head_stride;
+  d.norm_page_stride = w.norm_page_stride;
+  d.norm_head_stride = w.norm_head_stride;
+  d.Pi = w.Pi;
+  d.centroids = w.centroids;
+  d.bw = w.bw;
+  d.nb = D * w.bw / 8;
+  return w.pages && w.norms && w.Pi && w.centroids;
+}
+
+}  // namespace
+
+extern "C" size_t wtq_decode_counter_bytes(int B, int Hkv) {
+  return round_up((size_t)(B > 0 ? B : 0) * (size_t)(Hkv > 0 ? Hkv : 0) * sizeof(int32_t), 256);
+}
+
+extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pages, int S,
+                                      int bw_k, int bw_v) {
+  (void)Hq; (void)D; (void)bw_k; (void)bw_v;
+  if (B < 1 || Hkv < 1) return 1;
+  // aim for about eight 128-thread blocks per SM
+  const int64_t want = (int64_t)device_sms() * 8;
+  const int64_t have = (int64_t)B * Hkv;
+  int splits = (int)((want + have - 1) / have);
+  return clamp_splits(splits, max_pages, S);
+}
+
+extern "C" size_t wtq_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_pages, int S,
+                                             int num_splits) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || D < 1) return 256;
+  int splits = num_splits > 0 ? clamp_splits(num_splits, max_pages, S)
+                              : wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 8, 8);
+  const size_t rows = (size_t)B * Hq;
+  size_t bytes = wtq_decode_counter_bytes(B, Hkv);
+  bytes += round_up(rows * D * sizeof(float), 256);                   // rotated query
+  bytes += round_up(rows * splits * D * sizeof(float), 256);          // partial acc
+  bytes += 2 * round_up(rows * splits * sizeof(float), 256);          // partial m, l
+  return bytes;
+}
+
+extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], void *out,
+                          const int64_t out_strides[2], const wtq_side_t *k_side,
+                          const wtq_side_t *v_side, const int32_t *page_table,
+                          int64_t table_stride, const int32_t *seq_lens, float scale, int B,
+                          int Hq, int Hkv, int D, int S, int P, int max_pages, int num_splits,
+                          void *workspace, size_t workspace_bytes, int32_t *status,
+                          void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (B < 0 || Hq < 1 || Hkv < 1 || S < 1 || P < 1 || max_pages < 1)
+    return fail(WTQ_ERR_ARG, "wtq_decode: bad sizes");
+  if (Hq % Hkv) return fail(WTQ_ERR_ARG, "wtq_decode: Hq=%d is not a multiple of Hkv=%d", Hq, Hkv);
+  if (D < 1 || D > 256) return fail(WTQ_ERR_ARG, "wtq_decode: need 1 <= head_dim <= 256");
+  if (dtype < WTQ_F32 || dtype > WTQ_BF16) return fail(WTQ_ERR_ARG, "wtq_decode: bad dtype");
+  if (!k_side || !v_side || !q_strides || !out_strides)
+    return fail(WTQ_ERR_ARG, "wtq_decode: null descriptor");
+  for (const wtq_side_t *w : {k_side, v_side})
+    if (!width_supported(w->bw) || (D * w->bw) % 8)
+      return fail(WTQ_ERR_ARG, "wtq_decode: bit width %d unsupported for head_dim %d", w->bw, D);
+  if (B == 0) return WTQ_OK;
+  DecodeParams p;
+  if (!fill_side(p.k, *k_side, D) || !fill_side(p.v, *v_side, D))
+    return fail(WTQ_ERR_ARG, "wtq_decode: null pages, norms, Pi or centroids");
+  if (!q || !out || !page_table || !seq_lens || !workspace)
+    return fail(WTQ_ERR_ARG, "wtq_decode: null input");
+  const int splits = num_splits > 0 ? clamp_splits(num_splits, max_pages, S)
+                                    : wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S,
+                                                             k_side->bw, v_side->bw);
+  const size_t need = wtq_decode_workspace_bytes(B, Hq, Hkv, D, max_pages, S, splits);
+  if (workspace_bytes < need)
+    return fail(WTQ_ERR_WORKSPACE, "wtq_decode: workspace %zu < %zu bytes", workspace_bytes, need);
+
+  const size_t rows = (size_t)B * Hq;
+  char *ws = (char *)workspace + wtq_decode_counter_bytes(B, Hkv);
+  float *q_rot = (float *)ws;
+  ws += round_up(rows * D * sizeof(float), 256);
+  p.part_acc = (float *)ws;
+  ws += round_up(rows * splits * D * sizeof(float), 256);
+  p.part_m = (float *)ws;
+  ws += round_up(rows * splits * sizeof(float), 256);
+  p.part_l = (float *)ws;
+
+  p.q_rot = q_rot;
+  p.page_table = page_table;
+  p.table_stride = table_stride;
+  p.seq_lens = seq_lens;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.n_rep = Hq / Hkv; p.D = D; p.S = S; p.P = P;
+  p.max_pages = max_pages; p.num_splits = splits; p.status = status;
+
+  if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, scale, B, Hq, D, q_rot, stream))
+    return rc;
+  if (int rc = launch_decode_generic(p, stream)) return rc;
+  MergeParams m;
+  m.part_acc = p.part_acc; m.part_m = p.part_m; m.part_l = p.part_l;
+  m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
+  m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
+  return launch_merge(m, B, stream);
+}

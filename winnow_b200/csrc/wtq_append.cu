@@ -1,0 +1,300 @@
+// Fused append: rotate -> norm -> Lloyd-Max quantize -> bit-pack -> page scatter.
+//
+// One thread block owns one vector at a time and one rotation matrix for its
+// whole life (grid.y picks the K or V side), so Pi is staged in shared memory
+// once per block and every vector after that costs D chained FMAs per thread.
+//
+// Arithmetic contract (bit-exactness with the reference's CPU PyTorch path,
+// turboquant_kv/cache.py:108-115).  Every operation below is an explicit
+// round-to-nearest intrinsic so no compiler flag can fuse or reorder it:
+//   norm     : 8 interleaved partial sums (partial j takes d = j mod 8), each
+//              step round(x*x) then round(acc + .), partials added left to
+//              right, IEEE sqrt, clamp at 1e-10;
+//   x / norm : IEEE division;
+//   rotation : WTQ_ORDER_SEQUENTIAL    one FMA chain per output, d ascending;
+//              WTQ_ORDER_INTERLEAVED16 16 chains (chain j takes d = j mod 16),
+//              ((c[j]+c[j+4])+c[j+8])+c[j+12] for j = 0..3, then
+//              (s0+s1)+(s2+s3);
+//   bucket   : number of boundaries strictly below y (bucketize, right=False);
+//   norm out : fp16 round-to-nearest-even for pages, fp32 for wtq_quantize.
+#include "wtq_common.cuh"
+
+namespace wtq {
+
+struct QuantSideDev {
+  const float *Pi;
+  const float *bounds;
+  int bw, nb, nbounds;
+};
+
+struct QuantScratch {
+  float x[256];
+  float lane[8];
+  float norm;
+  float bounds[255];
+  uint8_t idx[256];
+};
+
+template <bool STAGE>
+__device__ __forceinline__ float pi_at(const float *pi_s, const float *pi_g, int D, int c, int d) {
+  return STAGE ? pi_s[c * (D + 1) + d] : pi_g[(int64_t)c * D + d];
+}
+
+// All threads of the block call this.  On return scratch.idx holds the D codes
+// and scratch.norm the clamped fp32 norm; the caller synchronises before use.
+template <bool STAGE>
+__device__ void quantize_vector(QuantScratch &s, const float *pi_s, const QuantSideDev &q, int D,
+                                int order) {
+  const int c = threadIdx.x;
+  if (c < 8) {
+    float acc = 0.0f;
+    for (int d = c; d < D; d += 8) acc = __fadd_rn(acc, __fmul_rn(s.x[d], s.x[d]));
+    s.lane[c] = acc;
+  }
+  __syncthreads();
+  if (c == 0) {
+    float t = s.lane[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) t = __fadd_rn(t, s.lane[j]);
+    s.norm = fmaxf(__fsqrt_rn(t), 1e-10f);
+  }
+  __syncthreads();
+  if (c < D) s.x[c] = __fdiv_rn(s.x[c], s.norm);
+  __syncthreads();
+  if (c < D) {
+    float y;
+    if (order == WTQ_ORDER_INTERLEAVED16) {
+      float ch[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) ch[j] = 0.0f;
+      for (int d0 = 0; d0 < D; d0 += 16) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (d0 + j < D)
+            ch[j] = __fmaf_rn(s.x[d0 + j], pi_at<STAGE>(pi_s, q.Pi, D, c, d0 + j), ch[j]);
+      }
+      float part[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        part[j] = __fadd_rn(__fadd_rn(__fadd_rn(ch[j], ch[j + 4]), ch[j + 8]), ch[j + 12]);
+      y = __fadd_rn(__fadd_rn(part[0], part[1]), __fadd_rn(part[2], part[3]));
+    } else {
+      float acc = 0.0f;
+#pragma unroll 8
+      for (int d = 0; d < D; ++d) acc = __fmaf_rn(s.x[d], pi_at<STAGE>(pi_s, q.Pi, D, c, d), acc);
+      y = acc;
+    }
+    int lo = 0, hi = q.nbounds;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (s.bounds[mid] < y) lo = mid + 1;
+      else hi = mid;
+    }
+    s.idx[c] = (uint8_t)lo;
+  }
+}
+
+__device__ __forceinline__ uint8_t packed_byte(const uint8_t *idx, int j, int bw) {
+  if (bw == 8) return idx[j];
+  if (bw == 4) return (uint8_t)(idx[2 * j] | (idx[2 * j + 1] << 4));
+  unsigned out = 0;
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    const int bit = 8 * j + b;
+    const int i = bit / bw;
+    out |= ((idx[i] >> (bit - i * bw)) & 1u) << b;
+  }
+  return (uint8_t)out;
+}
+
+template <bool STAGE>
+__device__ void stage_side(float *pi_s, QuantScratch &s, const QuantSideDev &q, int D) {
+  if (STAGE) {
+    for (int e = threadIdx.x; e < D * D; e += blockDim.x) {
+      const int r = e / D, col = e - r * D;
+      pi_s[r * (D + 1) + col] = q.Pi[e];
+    }
+  }
+  for (int e = threadIdx.x; e < q.nbounds; e += blockDim.x) s.bounds[e] = q.bounds[e];
+  __syncthreads();
+}
+
+struct QuantizeParams {
+  const void *x;
+  int dtype;
+  int64_t rows, row_stride;
+  int D, order;
+  QuantSideDev side;
+  uint8_t *idx, *packed;
+  float *norms;
+};
+
+template <bool STAGE>
+__global__ void quantize_kernel(QuantizeParams p) {
+  extern __shared__ float pi_s[];
+  __shared__ QuantScratch s;
+  stage_side<STAGE>(pi_s, s, p.side, p.D);
+  const int c = threadIdx.x;
+  for (int64_t r = blockIdx.x; r < p.rows; r += gridDim.x) {
+    if (c < p.D) s.x[c] = load_as_float(p.x, r * p.row_stride + c, p.dtype);
+    __syncthreads();
+    quantize_vector<STAGE>(s, pi_s, p.side, p.D, p.order);
+    __syncthreads();
+    if (p.idx && c < p.D) p.idx[r * p.D + c] = s.idx[c];
+    if (p.packed && c < p.side.nb) p.packed[r * p.side.nb + c] = packed_byte(s.idx, c, p.side.bw);
+    if (p.norms && c == 0) p.norms[r] = s.norm;
+    __syncthreads();
+  }
+}
+
+struct AppendSideDev {
+  QuantSideDev q;
+  const void *src;
+  int64_t sb, sh, st;  // element strides: batch, head, token
+  uint8_t *pages;
+  __half *norms;
+  int64_t page_stride, head_stride, norm_page_stride, norm_head_stride;
+};
+
+struct AppendParams {
+  AppendSideDev side[2];
+  const int32_t *page_table;
+  int64_t table_stride;
+  const int32_t *seq_lens;
+  int dtype, B, Hkv, n, D, S, P, max_pages, order;
+  int32_t *status;
+};
+
+template <bool STAGE>
+__global__ void append_kernel(AppendParams p) {
+  extern __shared__ float pi_s[];
+  __shared__ QuantScratch s;
+  __shared__ int64_t dest[2];
+  const AppendSideDev &a = p.side[blockIdx.y];
+  stage_side<STAGE>(pi_s, s, a.q, p.D);
+  const int c = threadIdx.x;
+  const int64_t vectors = (int64_t)p.B * p.Hkv * p.n;
+  for (int64_t vec = blockIdx.x; vec < vectors; vec += gridDim.x) {
+    const int i = (int)(vec % p.n);
+    const int h = (int)((vec / p.n) % p.Hkv);
+    const int b = (int)(vec / ((int64_t)p.n * p.Hkv));
+    if (c == 0) {
+      // Where the token goes; -1 marks a position or page the table does not
+      // cover, which is reported through `status` and not written.
+      const int pos = p.seq_lens[b] - p.n + i;
+      int64_t code_off = -1, norm_off = -1;
+      const int slot_page = pos >= 0 ? pos / p.S : -1;
+      if (pos < 0 || slot_page >= p.max_pages) {
+        if (p.status) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+      } else {
+        const int pid = p.page_table[(int64_t)b * p.table_stride + slot_page];
+        if (pid < 0 || pid >= p.P) {
+          if (p.status) atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+        } else {
+          const int slot = pos - slot_page * p.S;
+          code_off = (int64_t)pid * a.page_stride + (int64_t)h * a.head_stride +
+                     (int64_t)slot * a.q.nb;
+          norm_off = (int64_t)pid * a.norm_page_stride + (int64_t)h * a.norm_head_stride + slot;
+        }
+      }
+      dest[0] = code_off;
+      dest[1] = norm_off;
+    }
+    if (c < p.D)
+      s.x[c] = load_as_float(a.src, (int64_t)b * a.sb + (int64_t)h * a.sh + (int64_t)i * a.st + c,
+                             p.dtype);
+    __syncthreads();
+    quantize_vector<STAGE>(s, pi_s, a.q, p.D, p.order);
+    __syncthreads();
+    if (dest[0] >= 0) {
+      if (c < a.q.nb) a.pages[dest[0] + c] = packed_byte(s.idx, c, a.q.bw);
+      if (c == 0) a.norms[dest[1]] = __float2half_rn(s.norm);
+    }
+    __syncthreads();
+  }
+}
+
+static int block_threads(int D) { return ((D + 31) / 32) * 32; }
+
+template <typename K, typename P>
+static int launch_staged(K staged, K direct, P &params, int D, int64_t work, int sides,
+                         cudaStream_t stream, const char *what) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const bool stage = D <= 128;
+  const size_t smem = stage ? (size_t)D * (D + 1) * sizeof(float) : 0;
+  if (stage && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(staged, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return check_cuda(e, what);
+  }
+  int64_t blocks = work < (int64_t)sms * 3 ? work : (int64_t)sms * 3;
+  if (blocks < 1) blocks = 1;
+  dim3 grid((unsigned)blocks, (unsigned)sides);
+  if (stage) staged<<<grid, block_threads(D), smem, stream>>>(params);
+  else direct<<<grid, block_threads(D), 0, stream>>>(params);
+  return check_cuda(cudaGetLastError(), what);
+}
+
+}  // namespace wtq
+
+using namespace wtq;
+
+extern "C" int wtq_quantize(const void *x, int dtype, int64_t rows, int64_t row_stride, int D,
+                            const float *Pi, const float *bounds, int bw, int order,
+                            uint8_t *idx, uint8_t *packed, float *norms, void *stream) {
+  if (rows < 0 || D < 1 || D > 256) return fail(WTQ_ERR_ARG, "wtq_quantize: need 1 <= D <= 256");
+  if (!width_supported(bw) || (D * bw) % 8)
+    return fail(WTQ_ERR_ARG, "wtq_quantize: bit width %d unsupported for D=%d", bw, D);
+  if (dtype < WTQ_F32 || dtype > WTQ_BF16) return fail(WTQ_ERR_ARG, "wtq_quantize: bad dtype");
+  if (rows == 0) return WTQ_OK;
+  if (!x || !Pi || !bounds) return fail(WTQ_ERR_ARG, "wtq_quantize: null input");
+  QuantizeParams p;
+  p.x = x; p.dtype = dtype; p.rows = rows; p.row_stride = row_stride; p.D = D;
+  p.order = resolve_order(order, rows);
+  p.side = {Pi, bounds, bw, D * bw / 8, (1 << bw) - 1};
+  p.idx = idx; p.packed = packed; p.norms = norms;
+  return launch_staged(quantize_kernel<true>, quantize_kernel<false>, p, D, rows, 1,
+                       (cudaStream_t)stream, "wtq_quantize launch");
+}
+
+extern "C" int wtq_append(const void *k, const void *v, int dtype, const int64_t k_strides[3],
+                          const int64_t v_strides[3], const wtq_side_t *k_side,
+                          const wtq_side_t *v_side, const int32_t *page_table,
+                          int64_t table_stride, const int32_t *seq_lens, int B, int Hkv, int n,
+                          int D, int S, int P, int max_pages, int order, int32_t *status,
+                          void *stream) {
+  if (B < 0 || Hkv < 1 || n < 0 || S < 1 || P < 1 || max_pages < 1)
+    return fail(WTQ_ERR_ARG, "wtq_append: bad sizes");
+  if (D < 1 || D > 256) return fail(WTQ_ERR_ARG, "wtq_append: need 1 <= D <= 256");
+  if (dtype < WTQ_F32 || dtype > WTQ_BF16) return fail(WTQ_ERR_ARG, "wtq_append: bad dtype");
+  if (!k_side || !v_side || !k_strides || !v_strides)
+    return fail(WTQ_ERR_ARG, "wtq_append: null descriptor");
+  const wtq_side_t *sides[2] = {k_side, v_side};
+  const void *src[2] = {k, v};
+  const int64_t *strides[2] = {k_strides, v_strides};
+  AppendParams p;
+  for (int s = 0; s < 2; ++s) {
+    const wtq_side_t &w = *sides[s];
+    if (!width_supported(w.bw) || (D * w.bw) % 8)
+      return fail(WTQ_ERR_ARG, "wtq_append: bit width %d unsupported for D=%d", w.bw, D);
+    if (!w.pages || !w.norms || !w.Pi || !w.bounds)
+      return fail(WTQ_ERR_ARG, "wtq_append: null pages, norms, Pi or bounds");
+    AppendSideDev &a = p.side[s];
+    a.q = {w.Pi, w.bounds, w.bw, D * w.bw / 8, (1 << w.bw) - 1};
+    a.src = src[s];
+    a.sb = strides[s][0]; a.sh = strides[s][1]; a.st = strides[s][2];
+    a.pages = w.pages; a.norms = (__half *)w.norms;
+    a.page_stride = w.page_stride; a.head_stride = w.head_stride;
+    a.norm_page_stride = w.norm_page_stride; a.norm_head_stride = w.norm_head_stride;
+  }
+  const int64_t vectors = (int64_t)B * Hkv * n;
+  if (vectors == 0) return WTQ_OK;
+  if (!k || !v || !page_table || !seq_lens) return fail(WTQ_ERR_ARG, "wtq_append: null input");
+  p.page_table = page_table; p.table_stride = table_stride; p.seq_lens = seq_lens;
+  p.dtype = dtype; p.B = B; p.Hkv = Hkv; p.n = n; p.D = D; p.S = S; p.P = P;
+  p.max_pages = max_pages; p.order = resolve_order(order, vectors); p.status = status;
+  return launch_staged(append_kernel<true>, append_kernel<false>, p, D, vectors, 2,
+                       (cudaStream_t)stream, "wtq_append launch");
+}

@@ -1,0 +1,46 @@
+// Parameter blocks shared by the decode kernels and their host launcher.
+#pragma once
+
+#include "wtq_common.cuh"
+
+namespace wtq {
+
+constexpr int kMaxSplits = 256;
+
+struct DecodeSideDev {
+  const uint8_t *pages;
+  const __half *norms;
+  int64_t page_stride, head_stride;            // bytes
+  int64_t norm_page_stride, norm_head_stride;  // elements
+  const float *Pi;
+  const float *centroids;
+  int bw, nb;
+};
+
+struct DecodeParams {
+  DecodeSideDev k, v;
+  const float *q_rot;  // (B, Hq, D) fp32, already scaled
+  const int32_t *page_table;
+  int64_t table_stride;
+  const int32_t *seq_lens;
+  int B, Hq, Hkv, n_rep, D, S, P, max_pages, num_splits;
+  float *part_acc;  // (B, Hq, splits, D)
+  float *part_m;    // (B, Hq, splits)
+  float *part_l;
+  int32_t *status;
+};
+
+struct MergeParams {
+  const float *part_acc, *part_m, *part_l;
+  const float *Pi_v;
+  void *out;
+  int64_t osb, osh;
+  int dtype, Hq, D, num_splits;
+};
+
+int launch_rotate_q(const void *q, int dtype, const int64_t *q_strides, const float *Pi,
+                    float scale, int B, int Hq, int D, float *q_rot, cudaStream_t stream);
+int launch_decode_generic(const DecodeParams &p, cudaStream_t stream);
+int launch_merge(const MergeParams &p, int B, cudaStream_t stream);
+
+}  // namespace wtq

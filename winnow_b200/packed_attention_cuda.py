@@ -1,0 +1,111 @@
+"""Decode attention over paged packed K/V on the CUDA backend.
+
+Counterpart of the reference's Triton operator
+(turboquant_kv/packed_attention_triton.py:166-262) with its call signature:
+one query token per sequence, `q` (B, Hq, 1, D) in any float dtype, result
+(B, Hq, 1, D) in `q.dtype`, fp32 inside.  The query rotation, the split-K scan
+of the page table and the merge with the output rotation all run inside
+libwinnow_tq (wtq_decode); the only allocations are the result and one
+workspace whose size depends on batch, heads and splits, never on history
+length.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from . import packed_attention as pa
+
+
+def check_kernel_contract(q: torch.Tensor, kv: pa.PackedKV, *, check_page_ids: bool = True) -> None:
+    pa.check_contract(q, kv, check_page_ids=check_page_ids)
+    if q.shape[2] != 1:
+        raise pa.UnsupportedLayout("the CUDA decode kernel serves one query token per sequence")
+    if not q.is_cuda:
+        raise pa.UnsupportedLayout("the CUDA decode kernel needs CUDA tensors")
+    if q.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise pa.UnsupportedLayout(f"q dtype {q.dtype} is not a supported float type")
+    if kv.head_dim > 256:
+        raise pa.UnsupportedLayout("head_dim above 256 is not supported")
+    for name, pages, norms in (("k", kv.k_pages, kv.k_norms), ("v", kv.v_pages, kv.v_norms)):
+        if pages.stride(-1) != 1 or pages.stride(-2) != pages.shape[-1] or norms.stride(-1) != 1:
+            raise pa.UnsupportedLayout(f"{name} pages need contiguous (S, NB) rows and contiguous "
+                                       "norm slots")
+    if kv.page_table.stride(-1) != 1 or not kv.seq_lens.is_contiguous():
+        raise pa.UnsupportedLayout("page_table rows and seq_lens must be contiguous")
+    for quant in (kv.k_quant, kv.v_quant):
+        if not quant.Pi.is_contiguous() or not quant.centroids.is_contiguous():
+            raise pa.UnsupportedLayout("rotations and codebooks must be contiguous")
+
+
+def _side(pages, norms, quant, bounds=None) -> _lib.Side:
+    return _lib.Side(pages.data_ptr(), norms.data_ptr(), pages.stride(0), pages.stride(1),
+                     norms.stride(0), norms.stride(1), quant.Pi.data_ptr(),
+                     bounds.data_ptr() if bounds is not None else None,
+                     quant.centroids.data_ptr() if quant.centroids is not None else None,
+                     quant.bit_width)
+
+
+def decode_workspace(B: int, Hq: int, Hkv: int, D: int, max_pages: int, S: int,
+                     num_splits: int, device) -> torch.Tensor:
+    """Workspace for one call; its leading counter block starts zeroed."""
+    L = _lib.lib()
+    size = L.wtq_decode_workspace_bytes(B, Hq, Hkv, D, max_pages, S, num_splits)
+    ws = torch.empty(size, dtype=torch.uint8, device=device)
+    ws[: L.wtq_decode_counter_bytes(B, Hkv)].zero_()
+    return ws
+
+
+@torch.no_grad()
+def packed_decode_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
+                            num_splits: int | None = None, allow_tf32: bool = False,
+                            num_warps: int = 4, num_stages: int = 2, pages_per_iter: int = 1,
+                            check_page_ids: bool = True, out: torch.Tensor | None = None,
+                            workspace: torch.Tensor | None = None,
+                            status: torch.Tensor | None = None) -> torch.Tensor:
+    """q (B, Hq, 1, D) -> (B, Hq, 1, D) in q.dtype.
+
+    `num_splits=None` (or 0) lets the backend size the split-K grid; a positive
+    value is honoured.  `allow_tf32`, `num_warps`, `num_stages` and
+    `pages_per_iter` are accepted for call compatibility with the Triton
+    operator; only `pages_per_iter` is validated (a power of two), none changes
+    the CUDA schedule.  `out` may be a (B, Hq, 1, D) view into a larger buffer
+    (e.g. this rank's heads inside a gathered output) with unit stride in D.
+    """
+    check_kernel_contract(q, kv, check_page_ids=check_page_ids)
+    if pages_per_iter < 1 or pages_per_iter & (pages_per_iter - 1):
+        raise pa.UnsupportedLayout("pages_per_iter must be a power of two >= 1")
+    del allow_tf32, num_warps, num_stages
+    B, Hq, _, D = q.shape
+    dev = q.device
+    Hkv, S, P = kv.num_kv_heads, kv.page_size, kv.k_pages.shape[0]
+    max_pages = kv.page_table.shape[1]
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    if out is None:
+        out = torch.empty(B, Hq, 1, D, dtype=q.dtype, device=dev)
+    elif tuple(out.shape) != (B, Hq, 1, D) or out.dtype != q.dtype or out.stride(-1) != 1 \
+            or out.device != dev:
+        raise pa.UnsupportedLayout("out must be (B, Hq, 1, D) in q.dtype with unit stride in D")
+    if B == 0:
+        return out
+    if max_pages == 0:
+        return out.zero_()
+    L = _lib.lib()
+    splits = int(num_splits or 0)
+    if workspace is None:
+        workspace = decode_workspace(B, Hq, Hkv, D, max_pages, S, splits, dev)
+    k_side = _side(kv.k_pages, kv.k_norms, kv.k_quant)
+    v_side = _side(kv.v_pages, kv.v_norms, kv.v_quant)
+    with torch.cuda.device(dev):
+        _lib.check(L.wtq_decode(
+            q.data_ptr(), _lib.dtype_code(q.dtype), _lib.i64x(q.stride(0), q.stride(1)),
+            out.data_ptr(), _lib.i64x(out.stride(0), out.stride(1)),
+            ctypes.byref(k_side), ctypes.byref(v_side),
+            kv.page_table.data_ptr(), kv.page_table.stride(0), kv.seq_lens.data_ptr(),
+            float(scale), B, Hq, Hkv, D, S, P, max_pages, splits,
+            workspace.data_ptr(), workspace.numel(),
+            status.data_ptr() if status is not None else None, _lib.stream_ptr(dev)))
+    return out
