@@ -1,0 +1,451 @@
+"""Benchmark of the packed decode-attention step (one layer, one query token per
+sequence) on B200, with the roofline of its page-scan kernel and a CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload config2]
+    python bench.py --impl reference ...      # CPU oracle port on the host cores
+
+N > 1 is launched by torchrun, one rank per GPU; KV heads (and their query
+heads) are sharded across ranks, each rank scans its own pages, and one
+all-gather of the outputs closes the step.  Rank 0 prints one JSON line.
+
+A step reads one layer's pages.  The pool holds several layers and consecutive
+steps walk through them, so the bytes a step reads were last touched several
+hundred MB ago: every step streams from HBM, not from L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from winnow_b200 import workloads  # noqa: E402
+
+METRIC = "packed_decode_attn_us_per_step"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:                                   # noqa: BLE001
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while a region is being timed."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=fd, stderr=subprocess.DEVNULL)
+            os.close(fd)
+            time.sleep(0.25)
+        except Exception:                                   # noqa: BLE001
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:                               # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in Path(self.path).read_text().splitlines():
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:                                   # noqa: BLE001
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        top = sorted(sm)[len(sm) // 2:]                      # the loaded half of the samples
+        return {"sm_mhz": statistics.median(top), "sm_max_mhz": max(mx),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------
+# distributed plumbing
+# --------------------------------------------------------------------------
+def init_ranks(gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    elif gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world, dev) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# --------------------------------------------------------------------------
+# workload construction (GPU arm)
+# --------------------------------------------------------------------------
+def build_gpu_cache(w, rank, world, layers, dev):
+    """This rank's shard of the packed pool: kv heads [rank*Hkv/world, ...)."""
+    from winnow_b200 import packed_attention as pa
+    from winnow_b200.cache import _get_quantizer
+    from winnow_b200.page_pool import PagePool
+
+    if w.kv_heads % world:
+        raise SystemExit(f"{w.kv_heads} kv heads do not shard over {world} ranks")
+    hkv = w.kv_heads // world
+    heads = slice(rank * hkv, (rank + 1) * hkv)
+    kq = _get_quantizer(w.bits_k, w.head_dim, dev, 42)
+    vq = _get_quantizer(w.bits_v, w.head_dim, dev, 43)
+    table, total = workloads.page_assignment(w)
+    S = w.page_size
+    pool = PagePool(num_layers=layers, num_pages=total, num_kv_heads=hkv, page_size=S,
+                    nb_k=w.head_dim * w.bits_k // 8, nb_v=w.head_dim * w.bits_v // 8, device=dev)
+    lens = w.seq_lens()
+    table_dev = table.to(dev)
+    for b, L in enumerate(lens):
+        k, v = workloads.dense_kv(w, b, heads)
+        k, v = k.to(dev), v.to(dev)
+        n_pg = -(-L // S)
+        ids = table_dev[b, :n_pg].long()
+        pad = n_pg * S - L
+        for layer in range(layers):
+            for dense, tq, pages, norms in ((k, kq, pool.k_pages, pool.k_norms),
+                                            (v, vq, pool.v_pages, pool.v_norms)):
+                # other layers hold the same vectors rotated along the token axis
+                src = dense if layer == 0 else dense.roll(17 * layer, dims=1)
+                codes, nrm = tq.quantize(src, packed=True)
+                if pad:
+                    codes = torch.nn.functional.pad(codes, (0, 0, 0, pad))
+                    nrm = torch.nn.functional.pad(nrm, (0, pad))
+                pages[layer][ids] = codes.view(hkv, n_pg, S, -1).permute(1, 0, 2, 3)
+                norms[layer][ids] = nrm.to(torch.float16).view(hkv, n_pg, S).permute(1, 0, 2)
+        del k, v
+    seq = torch.tensor(lens, dtype=torch.int32, device=dev)
+    handles = [pa.PackedKV(pool.k_pages[i], pool.k_norms[i], pool.v_pages[i], pool.v_norms[i],
+                           table_dev, seq, pa.Quantizer.from_tq(kq), pa.Quantizer.from_tq(vq),
+                           w.head_dim) for i in range(layers)]
+    return pool, handles, (kq, vq)
+
+
+def oracle_view(w, handle, seqs, kv_heads):
+    """CPU oracle cache over the first `seqs` sequences of a GPU handle."""
+    from oracle import tq_oracle as orc
+    table = handle.page_table[:seqs].cpu()
+    used = sorted({int(x) for x in table.flatten().tolist() if x >= 0})
+    remap = {p: i for i, p in enumerate(used)}
+    idx = torch.tensor(used, dtype=torch.long, device=handle.k_pages.device)
+    small = table.clone()
+    for r in range(small.shape[0]):
+        for c in range(small.shape[1]):
+            if small[r, c] >= 0:
+                small[r, c] = remap[int(small[r, c])]
+    return orc.OracleKV(handle.k_pages[idx][:, :kv_heads].cpu(), handle.k_norms[idx][:, :kv_heads].cpu(),
+                        handle.v_pages[idx][:, :kv_heads].cpu(), handle.v_norms[idx][:, :kv_heads].cpu(),
+                        small, handle.seq_lens[:seqs].cpu(),
+                        handle.k_quant.Pi.cpu(), handle.k_quant.centroids.cpu(), handle.k_quant.bit_width,
+                        handle.v_quant.Pi.cpu(), handle.v_quant.centroids.cpu(), handle.v_quant.bit_width,
+                        handle.head_dim)
+
+
+def time_cpu_port(q, okv, scale, reps):
+    from oracle import tq_oracle as orc
+    orc.tiled_attention(q, okv, scale)                       # warm-up
+    t = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        orc.tiled_attention(q, okv, scale)
+        t.append(time.perf_counter() - t0)
+    return statistics.median(t)
+
+
+# --------------------------------------------------------------------------
+# arms
+# --------------------------------------------------------------------------
+def run_ours(args):
+    from winnow_b200 import _lib
+    from winnow_b200.packed_attention_cuda import decode_workspace, packed_decode_attention
+
+    rank, world, local = init_ranks(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    w = workloads.WORKLOADS[args.workload]
+    lib = _lib.lib()
+    hq = w.q_heads // world
+    hkv = w.kv_heads // world
+    per_layer = sum(w.seq_lens()) * hkv * w.bytes_per_token_head()
+    layers = args.layers or max(2, min(16, -(-400_000_000 // max(per_layer, 1))))
+    pool, handles, _ = build_gpu_cache(w, rank, world, layers, dev)
+    scale = w.head_dim ** -0.5
+    q_full = workloads.queries(w)
+    q_host = q_full[:, rank * hq:(rank + 1) * hq].contiguous().pin_memory()
+    q_dev = q_host.to(dev)
+    B, D = w.batch, w.head_dim
+    max_pages = handles[0].page_table.shape[1]
+    ws = decode_workspace(B, hq, hkv, D, max_pages, w.page_size, args.splits, dev)
+    gathered = torch.empty(world, B, hq, 1, D, dtype=w.dtype, device=dev)
+    out_final = torch.empty(B, w.q_heads, 1, D, dtype=w.dtype, device=dev)
+    out_host = torch.empty(B, w.q_heads, 1, D, dtype=w.dtype).pin_memory()
+    if world > 1:
+        import torch.distributed as dist
+
+    def step(i, q):
+        kv = handles[i % layers]
+        if world == 1:
+            packed_decode_attention(q, kv, scale, num_splits=args.splits, check_page_ids=False,
+                                    out=out_final, workspace=ws)
+        else:
+            packed_decode_attention(q, kv, scale, num_splits=args.splits, check_page_ids=False,
+                                    out=gathered[rank], workspace=ws)
+            dist.all_gather_into_tensor(gathered.view(-1), gathered[rank].reshape(-1))
+            out_final.view(B, world, hq, 1, D).copy_(gathered.permute(1, 0, 2, 3, 4))
+        return out_final
+
+    # ---- parity spot check against the oracle (first sequence, rank 0's heads)
+    parity = None
+    if rank == 0 and not args.no_check:
+        from oracle import tq_oracle as orc
+        okv = oracle_view(w, handles[0], 1, hkv)
+        ref = orc.tiled_attention(q_full[:1, :hq].float(), okv, scale)
+        got = packed_decode_attention(q_dev[:1].contiguous(), _first_seq(handles[0]), scale,
+                                      check_page_ids=False)
+        parity = float((got.float().cpu() - ref).abs().max())
+
+    for i in range(args.warmup):
+        step(i, q_dev)
+    barrier(world)
+    launches0 = lib.wtq_launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        start.record()
+        for i in range(args.steps):
+            step(args.warmup + i, q_dev)
+        end.record()
+        barrier(world)
+        # second pass: same steps with events around the page-scan kernel only
+        lib.wtq_profile_enable(args.steps + 8)
+        for i in range(args.steps):
+            step(args.warmup + i, q_dev)
+        torch.cuda.synchronize()
+    launches = lib.wtq_launch_count() - launches0
+    import ctypes
+    k_ms, k_n = ctypes.c_double(0.0), ctypes.c_int(0)
+    lib.wtq_profile_collect(ctypes.byref(k_ms), ctypes.byref(k_n))
+    lib.wtq_profile_disable()
+    launches //= 2                                            # two passes of K steps
+    ms = max_over_ranks(start.elapsed_time(end) / args.steps, world, dev)
+    kernel_us = max_over_ranks(1e3 * k_ms.value / max(k_n.value, 1), world, dev)
+
+    # ---- end to end through the public call with host buffers
+    for i in range(min(args.warmup, 3)):
+        step(i, q_dev)
+    barrier(world)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        q_dev.copy_(q_host, non_blocking=True)
+        out_host.copy_(step(args.warmup + i, q_dev), non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / args.steps, world, dev)
+
+    # ---- fused append of one token per sequence (reported beside the step)
+    append_us = time_append(w, pool, handles, rank, world, dev, args)
+
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak()
+    alg_total = w.algorithmic_bytes()
+    alg_rank = w.algorithmic_bytes(kv_heads=hkv, q_heads=hq)
+    achieved = alg_rank / (kernel_us * 1e-6) / 1e9
+    cpu = None
+    if not args.no_cpu_baseline:
+        seqs = max(1, min(w.batch, args.cpu_seqs))
+        okv = oracle_view(w, handles[0], seqs, hkv)
+        t = time_cpu_port(q_full[:seqs, :hq].float(), okv, scale, reps=3)
+        frac = (sum(w.seq_lens()[:seqs]) * hkv) / (sum(w.seq_lens()) * w.kv_heads)
+        cpu = {"value": t * 1e6 / frac, "unit": "us", "cores": torch.get_num_threads(),
+               "kind": "port",
+               "sample": f"oracle tiled_attention, first {seqs} of {w.batch} sequences, "
+                         f"{hkv} of {w.kv_heads} kv heads, median of 3, scaled by tokens"}
+    line = {
+        "metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{w.name}: B{w.batch} Hq{w.q_heads} Hkv{w.kv_heads} D{w.head_dim} "
+                               f"ctx{w.context or 'ragged'} page{w.page_size} "
+                               f"{w.bits_k}-bit K/{w.bits_v}-bit V, q {str(w.dtype)[6:]}",
+                   "parallelism": f"kv-head tp{world}" if world > 1 else "single gpu",
+                   "l2": f"steps rotate over {layers} layers of pages "
+                         f"({layers * per_layer / 1e6:.0f} MB per GPU) so each step reads from HBM",
+                   "num_splits": args.splits or "auto"},
+        "hbm_gbs": alg_total / (ms * 1e-3) / 1e9,
+        "hbm_frac_of_8tbs_nominal": alg_total / (ms * 1e-3) / 1e9 / (NOMINAL_HBM_GBS * world),
+        "tokens_per_s": w.batch / (ms * 1e-3),
+        "append_us": append_us,
+        "e2e": {"value": e2e_ms * 1e3, "unit": "us",
+                "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
+                "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "page-scan kernel of wtq_decode", "kernel_us": kernel_us,
+                     "algorithmic_bytes_per_launch": alg_rank},
+        "cpu_baseline": cpu,
+        "clocks": clocks.summary(),
+        "parity_max_abs_err_vs_oracle": parity,
+    }
+    print(json.dumps(line))
+
+
+def _first_seq(handle):
+    from winnow_b200 import packed_attention as pa
+    return pa.PackedKV(handle.k_pages, handle.k_norms, handle.v_pages, handle.v_norms,
+                       handle.page_table[:1].contiguous(), handle.seq_lens[:1].contiguous(),
+                       handle.k_quant, handle.v_quant, handle.head_dim)
+
+
+def time_append(w, pool, handles, rank, world, dev, args):
+    """Median time of the fused append of one new token per sequence.  The
+    tokens overwrite the last stored position of every sequence with the vector
+    already there, so the cache the decode step reads is unchanged."""
+    from winnow_b200.cache import _get_quantizer
+    from winnow_b200.packed_backend import append_tokens
+    hkv = w.kv_heads // world
+    kq = _get_quantizer(w.bits_k, w.head_dim, dev, 42)
+    vq = _get_quantizer(w.bits_v, w.head_dim, dev, 43)
+    k, v = workloads.new_tokens(w)
+    k = k[:, rank * hkv:(rank + 1) * hkv].to(dev)
+    v = v[:, rank * hkv:(rank + 1) * hkv].to(dev)
+    spare = pool.k_pages.shape[0] - 1                          # scratch layer: the last one
+    kv = handles[spare]
+    times = []
+    for i in range(5 + 20):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        append_tokens(k, v, kv.k_pages, kv.k_norms, kv.v_pages, kv.v_norms, kv.page_table,
+                      kv.seq_lens, kq, vq)
+        e.record()
+        torch.cuda.synchronize()
+        if i >= 5:
+            times.append(s.elapsed_time(e) * 1e3)
+    return statistics.median(times)
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the step, as restated by the
+    oracle, on the host cores.  Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from oracle import tq_oracle as orc
+    w = workloads.WORKLOADS[args.workload]
+    seqs = max(1, min(w.batch, args.cpu_seqs))
+    kq = orc.OracleQuantizer.get(w.bits_k, w.head_dim, 42)
+    vq = orc.OracleQuantizer.get(w.bits_v, w.head_dim, 43)
+    lens = w.seq_lens()[:seqs]
+    ctx = min(max(lens), args.cpu_context)
+    lens = [min(L, ctx) for L in lens]
+    k = torch.zeros(seqs, w.kv_heads, ctx, w.head_dim)
+    v = torch.zeros_like(k)
+    for b in range(seqs):
+        kb, vb = workloads.dense_kv(w, b)
+        k[b, :, :lens[b]], v[b, :, :lens[b]] = kb[:, :lens[b]].float(), vb[:, :lens[b]].float()
+    okv = orc.pages_from_dense(k, v, lens, kq, vq, w.page_size,
+                               generator=torch.Generator().manual_seed(w.seed))
+    q = workloads.queries(w)[:seqs].float()
+    scale = w.head_dim ** -0.5
+    for _ in range(min(args.warmup, 2)):
+        orc.tiled_attention(q, okv, scale)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.tiled_attention(q, okv, scale)
+    per_step = (time.perf_counter() - t0) / args.steps
+    frac = sum(lens) / sum(w.seq_lens())
+    us = per_step * 1e6 / frac
+    sample = (f"oracle port of tiled_compressed_attention on {seqs} of {w.batch} sequences at "
+              f"context {ctx}, all {w.kv_heads} kv heads; time scaled by cached tokens to the full "
+              "workload")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": us, "unit": "us",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "parallelism": "host cpu"},
+        "cpu_baseline": {"value": us, "unit": "us", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config2", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--layers", type=int, default=0, help="layers of pages to rotate over (0=auto)")
+    ap.add_argument("--splits", type=int, default=0, help="split-K factor (0 = library's choice)")
+    ap.add_argument("--cpu-seqs", type=int, default=2)
+    ap.add_argument("--cpu-context", type=int, default=8192)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

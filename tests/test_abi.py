@@ -1,0 +1,60 @@
+"""The C-ABI library loads and exports every symbol the header declares.
+No compute call is made here (there may be no GPU)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from winnow_b200 import _build, _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def library():
+    if not _build.LIB.exists():
+        _build.build()
+    return ctypes.CDLL(str(_build.LIB))
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "winnow_tq.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(wtq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_entry_points():
+    names = declared_symbols()
+    for must in ("wtq_pack", "wtq_unpack", "wtq_quantize", "wtq_append", "wtq_decode",
+                 "wtq_decode_workspace_bytes", "wtq_dequant", "wtq_last_error", "wtq_version"):
+        assert must in names
+
+
+def test_every_declared_symbol_is_exported(library):
+    for name in declared_symbols():
+        assert hasattr(library, name), f"{name} declared in include/winnow_tq.h but not exported"
+
+
+def test_binding_covers_the_header():
+    assert set(declared_symbols()) == set(_lib.exported_symbols())
+
+
+def test_side_struct_matches_header():
+    # 2 pointers, 4 int64, 3 pointers, 1 int (+ padding)
+    assert ctypes.sizeof(_lib.Side) == 2 * 8 + 4 * 8 + 3 * 8 + 8
+
+
+def test_argument_errors_are_reported_without_a_gpu(library):
+    library.wtq_last_error.restype = ctypes.c_char_p
+    library.wtq_pack.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+                                 ctypes.c_int, ctypes.c_void_p]
+    assert library.wtq_pack(None, None, 4, 9, 3, None) == -1          # 27 bits: not whole bytes
+    assert b"multiple of 8" in library.wtq_last_error()
+    assert library.wtq_pack(None, None, 4, 128, 7, None) == -1        # width 7 unsupported
+    assert library.wtq_pack(None, None, 0, 128, 4, None) == 0         # empty input is fine
+    library.wtq_decode_workspace_bytes.restype = ctypes.c_size_t
+    library.wtq_decode_workspace_bytes.argtypes = [ctypes.c_int] * 7
+    small = library.wtq_decode_workspace_bytes(2, 8, 2, 128, 4, 16, 1)
+    big = library.wtq_decode_workspace_bytes(2, 8, 2, 128, 4096, 16, 8)
+    assert 0 < small < big

@@ -1,0 +1,219 @@
+"""GPU parity of packed decode attention: the CUDA path through the C ABI
+against the reference's stored outputs and the CPU oracle on the same bytes.
+Bounds: max-abs 2e-3 and relative L2 1e-3 (fp32 accumulation)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from helpers import ATOL, assert_attention_close, oracle_case, to_device
+from oracle import tq_oracle as orc
+from winnow_b200 import _lib, packed_attention as pa, packed_backend as pb, workloads
+from winnow_b200.cache import _get_quantizer, dequantize_rows
+from winnow_b200.packed_attention_cuda import packed_decode_attention
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("splits", [None, 1, 3])
+@pytest.mark.parametrize("c", cases.ATTENTION_CASES, ids=lambda c: c.name)
+def test_decode_matches_reference(golden, c, splits):
+    q, okv, _ = oracle_case(c)
+    ref = torch.from_numpy(golden("attention")[f"{c.name}/out"])
+    got = packed_decode_attention(q.to(DEV), to_device(okv, DEV), orc.default_scale(c.D),
+                                  num_splits=splits)
+    assert got.shape == q.shape and got.dtype == q.dtype
+    tol = ATOL * max(1.0, float(ref.abs().max()))
+    assert_attention_close(got, ref, atol=tol)
+    for b, L in enumerate(c.lens):
+        if L == 0:
+            assert (got[b] == 0).all()
+
+
+def test_config1_outputs(golden):
+    g = golden("config1")
+    w = workloads.WORKLOADS["config1"]
+    q = workloads.queries(w)
+    kq, vq = _get_quantizer(4, 128, DEV, 42), _get_quantizer(4, 128, DEV, 43)
+    kv = pa.PackedKV(*(torch.from_numpy(g[n]).to(DEV) for n in ("k_pages", "k_norms", "v_pages", "v_norms")),
+                     torch.from_numpy(g["page_table"]).to(DEV),
+                     torch.tensor(w.seq_lens(), dtype=torch.int32, device=DEV),
+                     pa.Quantizer.from_tq(kq), pa.Quantizer.from_tq(vq), 128)
+    got = packed_decode_attention(q.to(DEV), kv, pa.default_scale(128))
+    assert_attention_close(got, torch.from_numpy(g["out_tiled"]))
+    assert_attention_close(got, torch.from_numpy(g["out_reconstruct"]))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 3e-3)])
+def test_low_precision_query_dtype(dtype, tol):
+    c = cases.AttnCase("lp", 3, 2, 28, 4, 128, (60, 9), 16, 8, 8)
+    q, okv, _ = oracle_case(c)
+    ql = q.to(dtype)
+    got = packed_decode_attention(ql.to(DEV), to_device(okv, DEV), orc.default_scale(128))
+    assert got.dtype == dtype
+    ref = orc.tiled_attention(ql.float(), okv, orc.default_scale(128))
+    assert (got.float().cpu() - ref).abs().max() < tol
+
+
+def test_strided_pool_layer_view_and_output_slice():
+    """One layer of a (layers, P, ...) pool, storage offset > 0, and the result
+    written into a slice of a wider (B, Hq_total, 1, D) buffer."""
+    c = cases.AttnCase("strided", 4, 2, 8, 2, 64, (45, 20), 16, 8, 8)
+    q, okv, _ = oracle_case(c)
+    kv = to_device(okv, DEV)
+    mid = lambda t: torch.stack([torch.zeros_like(t), t, torch.zeros_like(t)])[1]
+    kv2 = pa.PackedKV(mid(kv.k_pages), mid(kv.k_norms), mid(kv.v_pages), mid(kv.v_norms),
+                      kv.page_table, kv.seq_lens, kv.k_quant, kv.v_quant, kv.head_dim)
+    assert kv2.k_pages.storage_offset() > 0
+    wide = torch.full((2, 24, 1, 64), 7.0, device=DEV)
+    out = packed_decode_attention(q.to(DEV), kv2, orc.default_scale(64), out=wide[:, 8:16])
+    ref = orc.tiled_attention(q, okv, orc.default_scale(64))
+    assert_attention_close(out, ref)
+    assert (wide[:, :8] == 7).all() and (wide[:, 16:] == 7).all()
+    assert_attention_close(wide[:, 8:16], ref)
+
+
+def test_rejects_before_launch():
+    c = cases.AttnCase("rej", 5, 2, 8, 2, 64, (20, 3), 16, 8, 8)
+    q, okv, _ = oracle_case(c)
+    kv = to_device(okv, DEV)
+    with pytest.raises(pa.UnsupportedLayout):
+        packed_decode_attention(q.repeat(1, 1, 2, 1).to(DEV), kv, 1.0)            # Q = 2
+    with pytest.raises(pa.UnsupportedLayout):
+        packed_decode_attention(q.to(DEV), kv, 1.0, pages_per_iter=3)
+    bad = pa.PackedKV(**{**kv.__dict__, "page_table": kv.page_table.clone()})
+    bad.page_table[0, 0] = kv.k_pages.shape[0]
+    with pytest.raises(pa.UnsupportedLayout):
+        packed_decode_attention(q.to(DEV), bad, 1.0)
+    # with the host check skipped the kernel itself refuses the id, flags it,
+    # and treats the page as masked instead of reading it
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = packed_decode_attention(q.to(DEV), bad, 1.0, check_page_ids=False, status=status)
+    assert int(status.item()) & _lib.STATUS_BAD_PAGE
+    assert torch.isfinite(out).all()
+
+
+def test_stale_slots_are_masked_not_trusted():
+    """Slots past seq_len hold garbage from a recycled page; results must not change."""
+    c = cases.AttnCase("stale", 9, 2, 8, 2, 128, (21, 5), 16, 4, 4)
+    q, okv, _ = oracle_case(c)
+    ref = orc.tiled_attention(q, okv, orc.default_scale(128))
+    kv = to_device(okv, DEV)
+    g = torch.Generator().manual_seed(1)
+    for b, L in enumerate(c.lens):
+        pid = int(okv.page_table[b, (L - 1) // 16])
+        kv.k_pages[pid, :, L % 16:] = torch.randint(0, 255, kv.k_pages[pid, :, L % 16:].shape,
+                                                    generator=g, dtype=torch.uint8).to(DEV)
+        kv.v_norms[pid, :, L % 16:] = float("inf")
+        kv.k_norms[pid, :, L % 16:] = 6e4
+    assert_attention_close(packed_decode_attention(q.to(DEV), kv, orc.default_scale(128)), ref)
+
+
+def test_workspace_is_independent_of_history_length():
+    L = _lib.lib()
+    a = L.wtq_decode_workspace_bytes(8, 28, 4, 128, 1024 // 32, 32, 4)
+    b = L.wtq_decode_workspace_bytes(8, 28, 4, 128, 16384 // 32, 32, 4)
+    assert a == b
+    assert b < 8 * 4 * 16384 * 128 * 2 / 50
+
+
+@pytest.mark.parametrize("bw", [4, 6, 8, 3])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dequant_golden(golden, bw, dtype):
+    g = golden("dequant")
+    tq = _get_quantizer(bw, 128, DEV, 42)
+    packed = torch.from_numpy(g[f"b{bw}/packed"]).to(DEV)
+    norms = torch.from_numpy(g[f"b{bw}/norms"]).to(DEV)
+    n = packed.shape[0]
+    guard = torch.full((n + 64, 128), -12352.0, dtype=dtype, device=DEV)    # canary tail
+    dequantize_rows(packed, norms, tq.centroids, tq.Pi, bw, 128, out=guard[:n])
+    ref = torch.from_numpy(g[f"b{bw}/out_f32"])
+    got = guard[:n].float().cpu()
+    assert (guard[n:] == -12352.0).all()
+    if dtype == torch.float32:
+        assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6 * float(ref.abs().max()))
+    else:
+        # at most one bf16 unit in the last place away from the rounded reference
+        rb = ref.to(torch.bfloat16).float()
+        ulp = (rb.abs() * 2.0 ** -7).clamp(min=1e-30)
+        assert ((got - rb).abs() <= ulp).all()
+
+
+def test_dequant_strided_cache_slice():
+    """(B, H, L, NB) view of a (B, H, MAXLEN, NB) buffer, read in place."""
+    B, H, MAXLEN, L, bw = 2, 3, 40, 27, 4
+    tq = _get_quantizer(bw, 128, DEV, 42)
+    g = torch.Generator().manual_seed(4)
+    buf = torch.randint(0, 256, (B, H, MAXLEN, 64), generator=g, dtype=torch.uint8)
+    nbuf = (torch.rand(B, H, MAXLEN, generator=g) * 50).half()
+    out = dequantize_rows(buf.to(DEV)[:, :, :L], nbuf.to(DEV)[:, :, :L], tq.centroids, tq.Pi, bw, 128,
+                          out=torch.empty(B, H, L, 128, device=DEV))
+    o = orc.OracleQuantizer.get(bw, 128, 42)
+    ref = orc.dequantize_rows(buf[:, :, :L].contiguous(), nbuf[:, :, :L].contiguous(),
+                              o.centroids, o.Pi, bw, 128)
+    assert torch.allclose(out.cpu(), ref, rtol=1e-5, atol=1e-5)
+
+
+def test_attention_interface_entry_point():
+    """winnow_packed_attention: decode goes to the CUDA operator, a prefill
+    chunk to dequantize + SDPA; both agree with the oracle."""
+    c = cases.AttnCase("iface", 21, 2, 8, 2, 128, (40, 17), 16, 4, 4)
+    k, v, q, g = cases.attention_inputs(c)
+    okv = orc.pages_from_dense(k, v, c.lens, orc.OracleQuantizer.get(4, 128, 42),
+                               orc.OracleQuantizer.get(4, 128, 43), 16, generator=g)
+    kv = to_device(okv, DEV)
+    pb.BACKEND_COUNTS.clear()
+    out, _ = pb.winnow_packed_attention(None, q.to(DEV), kv, kv, None, scaling=0.09)
+    assert out.shape == (2, 1, 8, 128) and pb.BACKEND_COUNTS["cuda_packed"] == 1
+    assert_attention_close(out.transpose(1, 2), orc.tiled_attention(q, okv, 0.09))
+    kv.decode_backend = "triton_packed"
+    pb.winnow_packed_attention(None, q.to(DEV), kv, kv, None, scaling=0.09)
+    assert pb.BACKEND_COUNTS["cuda_packed"] == 2 and pb.BACKEND_COUNTS["triton_packed"] == 1
+    gq = torch.Generator().manual_seed(5)
+    q5 = torch.randn(2, 8, 5, 128, generator=gq)
+    out5, _ = pb.winnow_packed_attention(None, q5.to(DEV), kv, kv, None, scaling=0.09)
+    assert pb.BACKEND_COUNTS["prefill_reconstruct_sdpa"] == 1
+    ref5 = orc.reconstruct_attention(q5, okv, 0.09)
+    assert (out5.transpose(1, 2).cpu() - ref5).abs().max() < 2e-3
+
+
+def test_append_then_decode_through_the_cache():
+    """One engine-style step: reserve pages, update() every layer, attend."""
+    from winnow_b200.page_pool import PagePool
+    B, Hq, Hkv, D, S = 3, 8, 2, 128, 16
+    lens = (33, 0, 16)
+    kq, vq = _get_quantizer(4, D, DEV, 42), _get_quantizer(6, D, DEV, 43)
+    oq, ov = orc.OracleQuantizer.get(4, D, 42), orc.OracleQuantizer.get(6, D, 43)
+    pool = PagePool(num_layers=1, num_pages=12, num_kv_heads=Hkv, page_size=S, nb_k=64, nb_v=96,
+                    device=DEV)
+    owners = ["a", "b", "c"]
+    g = torch.Generator().manual_seed(77)
+    hist_k = torch.randn(B, Hkv, 40, D, generator=g)
+    hist_v = torch.randn(B, Hkv, 40, D, generator=g)
+    # prefill each sequence alone (n = its length), then one batched decode step
+    for b, (o, L) in enumerate(zip(owners, lens)):
+        pool.ensure(o, L + 1)
+        if L:
+            cache = pb.PagedPackedCache(pool, [o], [0], k_quant=kq, v_quant=vq, head_dim=D)
+            cache.update(hist_k[b:b + 1, :, :L].to(DEV), hist_v[b:b + 1, :, :L].to(DEV), 0)
+    cache = pb.PagedPackedCache(pool, owners, list(lens), k_quant=kq, v_quant=vq, head_dim=D)
+    new_k = torch.randn(B, Hkv, 1, D, generator=g)
+    new_v = torch.randn(B, Hkv, 1, D, generator=g)
+    handle, _ = cache.update(new_k.to(DEV), new_v.to(DEV), 0)
+    q = torch.randn(B, Hq, 1, D, generator=g)
+    out, _ = pb.winnow_packed_attention(None, q.to(DEV), handle, handle, None)
+    # oracle: same pool layout, filled by the oracle's append
+    table = handle.page_table.cpu()
+    kp = torch.zeros(12, Hkv, S, 64, dtype=torch.uint8); vp = torch.zeros(12, Hkv, S, 96, dtype=torch.uint8)
+    kn = torch.zeros(12, Hkv, S, dtype=torch.float16); vn = torch.zeros(12, Hkv, S, dtype=torch.float16)
+    for b, L in enumerate(lens):
+        if L:
+            orc.append_tokens(kp, kn, vp, vn, table[b:b + 1], [0], hist_k[b:b + 1, :, :L],
+                              hist_v[b:b + 1, :, :L], oq, ov)
+    orc.append_tokens(kp, kn, vp, vn, table, lens, new_k, new_v, oq, ov)
+    assert torch.equal(pool.k_pages[0].cpu(), kp) and torch.equal(pool.v_pages[0].cpu(), vp)
+    assert torch.equal(pool.k_norms[0].cpu(), kn) and torch.equal(pool.v_norms[0].cpu(), vn)
+    okv = orc.OracleKV(kp, kn, vp, vn, table, torch.tensor([L + 1 for L in lens], dtype=torch.int32),
+                       oq.Pi, oq.centroids, 4, ov.Pi, ov.centroids, 6, D)
+    assert_attention_close(out.transpose(1, 2), orc.tiled_attention(q, okv, D ** -0.5))

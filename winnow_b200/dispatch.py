@@ -98,7 +98,7 @@ class Dispatcher:
                 or not 1 <= shape.head_dim <= 256:
             d = Decision("none", f"head_dim {shape.head_dim} at {shape.bit_width} bits is outside "
                          "the library's envelope", 1.0, ())
-        elif 0.0 < contract.max_abs_error < self.BACKEND_MAX_ABS_ERROR:
+        elif contract.max_abs_error < self.BACKEND_MAX_ABS_ERROR:
             d = Decision("none", "error budget below fp32 summation-order noise", 1.0, ())
         else:
             d = Decision(BACKEND, "single CUDA backend, fp32 accumulation", 1.0,
