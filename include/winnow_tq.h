@@ -137,6 +137,19 @@ int wtq_dequant(const uint8_t *packed, const void *norms_f16, const float *centr
                 const float *Pi, void *out, int out_dtype, int bw, int D, int64_t N, int64_t L,
                 int64_t MAXLEN, void *stream);
 
+/* Instrumentation; no counterpart in the reference.
+ * wtq_launch_count: kernels this library has launched in this process.
+ * wtq_profile_enable: from now on every wtq_decode call records a pair of CUDA
+ * events on its stream around its page-scan kernel (up to `capacity` calls).
+ * wtq_profile_collect waits for the recorded pairs, returns their summed
+ * duration in milliseconds and their number, and rearms the recorder.
+ * wtq_profile_disable releases the events.  Not meant for production use: the
+ * events serialise nothing, but enable/disable create and destroy them. */
+uint64_t wtq_launch_count(void);
+int wtq_profile_enable(int capacity);
+int wtq_profile_collect(double *total_ms, int *launches);
+int wtq_profile_disable(void);
+
 #ifdef __cplusplus
 }
 #endif

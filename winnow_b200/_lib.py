@@ -47,6 +47,10 @@ _SIGNATURES = {
                            ctypes.POINTER(c_int64), ctypes.POINTER(Side), ctypes.POINTER(Side),
                            c_void_p, c_int64, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "wtq_launch_count": (ctypes.c_uint64, []),
+    "wtq_profile_enable": (c_int, [c_int]),
+    "wtq_profile_collect": (c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
+    "wtq_profile_disable": (c_int, []),
     "wtq_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int64, c_int64, c_int64, c_void_p]),
 }

@@ -234,6 +234,7 @@ static int launch_staged(K staged, K direct, P &params, int D, int64_t work, int
   dim3 grid((unsigned)blocks, (unsigned)sides);
   if (stage) staged<<<grid, block_threads(D), smem, stream>>>(params);
   else direct<<<grid, block_threads(D), 0, stream>>>(params);
+  note_launches(1);
   return check_cuda(cudaGetLastError(), what);
 }
 

@@ -17,6 +17,11 @@ namespace wtq {
 char *error_buffer();
 int fail(int code, const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
+void note_launches(int n);
+// Recorder of event pairs around the decode page-scan kernel (see
+// wtq_profile_enable); both are no-ops while profiling is off.
+void profile_mark_begin(cudaStream_t stream);
+void profile_mark_end(cudaStream_t stream);
 
 inline bool width_supported(int bw) {
   return bw == 2 || bw == 3 || bw == 4 || bw == 5 || bw == 6 || bw == 8;

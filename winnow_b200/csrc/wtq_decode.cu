@@ -258,23 +258,28 @@ int launch_decode_generic(const DecodeParams &p, cudaStream_t stream) {
   const int nr = generic_group_width(p.n_rep);
   const int groups = (p.n_rep + nr - 1) / nr;
   dim3 grid((unsigned)p.num_splits, (unsigned)(p.Hkv * groups), (unsigned)p.B);
+  profile_mark_begin(stream);
   switch (nr) {
     case 1: decode_generic_kernel<1><<<grid, kTile, 0, stream>>>(p); break;
     case 2: decode_generic_kernel<2><<<grid, kTile, 0, stream>>>(p); break;
     case 4: decode_generic_kernel<4><<<grid, kTile, 0, stream>>>(p); break;
     default: decode_generic_kernel<8><<<grid, kTile, 0, stream>>>(p); break;
   }
+  profile_mark_end(stream);
+  note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_decode generic launch");
 }
 
 int launch_rotate_q(const void *q, int dtype, const int64_t *qs, const float *Pi, float scale,
                     int B, int Hq, int D, float *q_rot, cudaStream_t stream) {
   rotate_q_kernel<<<B * Hq, 128, 0, stream>>>(q, dtype, qs[0], qs[1], Pi, scale, Hq, D, q_rot);
+  note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_decode rotate launch");
 }
 
 int launch_merge(const MergeParams &p, int B, cudaStream_t stream) {
   merge_rotate_kernel<<<B * p.Hq, 128, 0, stream>>>(p);
+  note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_decode merge launch");
 }
 

@@ -80,5 +80,6 @@ extern "C" int wtq_dequant(const uint8_t *packed, const void *norms_f16, const f
   if (blocks > 148 * 8) blocks = 148 * 8;
   const int threads = D <= 32 ? 32 : D <= 64 ? 64 : 128;
   dequant_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(p);
+  note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_dequant launch");
 }

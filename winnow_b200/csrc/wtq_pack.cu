@@ -1,5 +1,9 @@
 // Bit-packing of codebook indices (LSB-first stream) and its inverse, plus the
 // library's error plumbing.
+#include <atomic>
+#include <mutex>
+#include <vector>
+
 #include "wtq_common.cuh"
 
 namespace wtq {
@@ -20,6 +24,38 @@ int fail(int code, const char *fmt, ...) {
 int check_cuda(cudaError_t e, const char *what) {
   if (e == cudaSuccess) return WTQ_OK;
   return fail(WTQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+static std::atomic<uint64_t> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+uint64_t launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
+
+static std::mutex g_profile_lock;
+static std::vector<cudaEvent_t> g_begin, g_end;
+static int g_recorded = 0;
+static bool g_open = false;
+
+void profile_mark_begin(cudaStream_t stream) {
+  std::lock_guard<std::mutex> hold(g_profile_lock);
+  if (g_recorded < (int)g_begin.size() && !g_open) {
+    cudaEventRecord(g_begin[g_recorded], stream);
+    g_open = true;
+  }
+}
+void profile_mark_end(cudaStream_t stream) {
+  std::lock_guard<std::mutex> hold(g_profile_lock);
+  if (g_open) {
+    cudaEventRecord(g_end[g_recorded++], stream);
+    g_open = false;
+  }
+}
+static void profile_release() {
+  for (cudaEvent_t e : g_begin) cudaEventDestroy(e);
+  for (cudaEvent_t e : g_end) cudaEventDestroy(e);
+  g_begin.clear();
+  g_end.clear();
+  g_recorded = 0;
+  g_open = false;
 }
 
 // One thread per output byte: byte j of a row gathers stream bits 8j..8j+7.
@@ -67,6 +103,46 @@ using namespace wtq;
 
 extern "C" int wtq_version(void) { return 100; }
 extern "C" const char *wtq_last_error(void) { return error_buffer(); }
+extern "C" uint64_t wtq_launch_count(void) { return launches_so_far(); }
+
+extern "C" int wtq_profile_enable(int capacity) {
+  if (capacity < 1) return fail(WTQ_ERR_ARG, "wtq_profile_enable: capacity must be positive");
+  std::lock_guard<std::mutex> hold(g_profile_lock);
+  profile_release();
+  for (int i = 0; i < capacity; ++i) {
+    cudaEvent_t b, e;
+    if (cudaEventCreate(&b) != cudaSuccess || cudaEventCreate(&e) != cudaSuccess) {
+      profile_release();
+      return check_cuda(cudaGetLastError(), "wtq_profile_enable");
+    }
+    g_begin.push_back(b);
+    g_end.push_back(e);
+  }
+  return WTQ_OK;
+}
+
+extern "C" int wtq_profile_collect(double *total_ms, int *launches) {
+  if (!total_ms || !launches) return fail(WTQ_ERR_ARG, "wtq_profile_collect: null output");
+  std::lock_guard<std::mutex> hold(g_profile_lock);
+  double sum = 0.0;
+  for (int i = 0; i < g_recorded; ++i) {
+    float ms = 0.0f;
+    cudaError_t e = cudaEventSynchronize(g_end[i]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, g_begin[i], g_end[i]);
+    if (e != cudaSuccess) return check_cuda(e, "wtq_profile_collect");
+    sum += ms;
+  }
+  *total_ms = sum;
+  *launches = g_recorded;
+  g_recorded = 0;
+  return WTQ_OK;
+}
+
+extern "C" int wtq_profile_disable(void) {
+  std::lock_guard<std::mutex> hold(g_profile_lock);
+  profile_release();
+  return WTQ_OK;
+}
 
 static int check_pack_args(const char *who, const void *a, const void *b, int64_t rows, int D,
                            int bw) {
@@ -84,6 +160,7 @@ extern "C" int wtq_pack(const uint8_t *idx, uint8_t *out, int64_t rows, int D, i
   if (rows == 0) return WTQ_OK;
   const int nb = D * bw / 8;
   pack_kernel<<<grid_for(rows * nb), 256, 0, (cudaStream_t)stream>>>(idx, out, rows, D, bw, nb);
+  note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_pack launch");
 }
 
@@ -93,5 +170,6 @@ extern "C" int wtq_unpack(const uint8_t *packed, uint8_t *idx, int64_t rows, int
   if (rows == 0) return WTQ_OK;
   const int nb = D * bw / 8;
   unpack_kernel<<<grid_for(rows * D), 256, 0, (cudaStream_t)stream>>>(packed, idx, rows, D, bw, nb);
+  note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_unpack launch");
 }
