@@ -1,5 +1,7 @@
 // Host entry points of wtq_decode: argument checks, workspace carving, launch
 // order.  Nothing here allocates or synchronises.
+#include <cstdlib>
+
 #include "wtq_decode.cuh"
 
 using namespace wtq;
@@ -29,6 +31,13 @@ int clamp_splits(int splits, int max_pages, int S) {
   return splits;
 }
 
+// WTQ_FORCE_GENERIC=1 in the environment routes every call through the generic
+// CUDA-core kernels (used by the tests to cover both paths on the same inputs).
+bool force_generic() {
+  const char *v = getenv("WTQ_FORCE_GENERIC");
+  return v && v[0] == '1';
+}
+
 bool fill_side(DecodeSideDev &d, const wtq_side_t &w, int D) {
   d.pages = w.pages;
   d.norms = (const __half *)w.norms;
@@ -51,20 +60,38 @@ extern "C" size_t wtq_decode_counter_bytes(int B, int Hkv) {
 
 extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pages, int S,
                                       int bw_k, int bw_v) {
-  (void)Hq; (void)D; (void)bw_k; (void)bw_v;
-  if (B < 1 || Hkv < 1) return 1;
-  // aim for about eight 128-thread blocks per SM
+  if (B < 1 || Hkv < 1 || Hq < 1) return 1;
+  const int64_t groups = (int64_t)B * Hkv;
+  const int64_t max_tokens = (int64_t)max_pages * S;
+  if (D == 128 && bw_k == 4 && bw_v == 4 && S % 16 == 0 && Hq / Hkv <= 8) {
+    // tensor-core path: every warp of the persistent grid (8 per SM) should see
+    // about three chunks, and a chunk should be long enough (>= 256 tokens)
+    // that writing its partial state stays small beside reading its pages
+    const int64_t workers = (int64_t)device_sms() * 8;
+    int64_t chunk = (max_tokens * groups + 3 * workers - 1) / (3 * workers);
+    chunk = (chunk + 63) / 64 * 64;
+    if (chunk < 256) chunk = 256;
+    if (chunk > 4096) chunk = 4096;
+    int64_t splits = (max_tokens + chunk - 1) / chunk;
+    if (splits > kMaxSplits) splits = kMaxSplits;
+    return clamp_splits((int)splits, max_pages, S);
+  }
+  // generic path: about eight 128-thread blocks per SM
   const int64_t want = (int64_t)device_sms() * 8;
-  const int64_t have = (int64_t)B * Hkv;
-  int splits = (int)((want + have - 1) / have);
-  return clamp_splits(splits, max_pages, S);
+  return clamp_splits((int)((want + groups - 1) / groups), max_pages, S);
 }
 
 extern "C" size_t wtq_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_pages, int S,
                                              int num_splits) {
   if (B < 1 || Hq < 1 || Hkv < 1 || D < 1) return 256;
-  int splits = num_splits > 0 ? clamp_splits(num_splits, max_pages, S)
-                              : wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 8, 8);
+  int splits;
+  if (num_splits > 0) {
+    splits = clamp_splits(num_splits, max_pages, S);
+  } else {                       // whichever kernel the call will pick, it fits
+    const int a = wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 4, 4);
+    const int b = wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 8, 8);
+    splits = a > b ? a : b;
+  }
   const size_t rows = (size_t)B * Hq;
   size_t bytes = wtq_decode_counter_bytes(B, Hkv);
   bytes += round_up(rows * D * sizeof(float), 256);                   // rotated query
@@ -121,12 +148,16 @@ extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], 
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.n_rep = Hq / Hkv; p.D = D; p.S = S; p.P = P;
   p.max_pages = max_pages; p.num_splits = splits; p.status = status;
 
-  if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, scale, B, Hq, D, q_rot, stream))
-    return rc;
-  if (int rc = launch_decode_generic(p, stream)) return rc;
   MergeParams m;
   m.part_acc = p.part_acc; m.part_m = p.part_m; m.part_l = p.part_l;
   m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
   m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
+  const bool fast = mma4_eligible(p) && !force_generic();
+  // the tensor-core path works in the exp2 domain: fold log2(e) into the query
+  const float q_scale = fast ? scale * 1.4426950408889634f : scale;
+  if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, q_scale, B, Hq, D, q_rot, stream))
+    return rc;
+  if (fast) return launch_decode_mma4(p, m, stream);
+  if (int rc = launch_decode_generic(p, stream)) return rc;
   return launch_merge(m, B, stream);
 }

@@ -1,0 +1,517 @@
+// Split-K decode attention over paged packed K/V: the sm_100a fast path for
+// head_dim 128, 4-bit keys and values, pages of a multiple of 16 tokens and a
+// GQA group of at most 8 query heads.
+//
+// One persistent CTA per SM, 8 warps.  A warp is an independent worker: it
+// takes (sequence, kv head, chunk of tokens) items round-robin, streams the
+// chunk's 16-token tiles from HBM into its private shared-memory ring with
+// 16-byte cp.async copies (the next 64 tokens are in flight while the current
+// 64 are consumed), and keeps the whole flash-decoding state in registers.
+//
+// Per 16-token tile, with the packed bytes never leaving registers/smem:
+//   scores   S^T[16 tok x 8 heads] = C_K[16 x 128] . Qrot^T   8 x mma.m16n8k16
+//   softmax  online, fp32, exp2 domain, max shared by shuffles
+//   values   O^T[128 d x 8 heads] += C_V^T[128 x 16 tok] . P'^T   8 x mma
+// The fp16 operands C_K / C_V are produced from the 4-bit codes by ONE
+// shared-memory lookup per packed byte (= two codes): a 256-entry table of
+// half2 {centroid[lo nibble], centroid[hi nibble]}, replicated per lane so
+// that every lookup of a warp is bank-conflict free, and placed at shared
+// address 0x10000 so that one byte-permute builds the address
+// (0x10000 | byte << 8 | table << 7 | lane << 2).
+//   * keys: a byte holds two adjacent coordinates of one token, which is the
+//     pair an A-fragment register of the score MMA wants (the contraction runs
+//     over coordinates, whose order is free: q is permuted to match);
+//   * values: the contraction runs over tokens, so a register must hold one
+//     coordinate of two tokens; the low (high) nibbles of the same byte of two
+//     tokens are merged by one shift and one bit-select into a byte that
+//     indexes the same table.
+// mma.sync is the right tensor instruction here: the operands are born in
+// registers; tcgen05 would need them written back to shared memory first.
+//
+// Reference schedule being reproduced: turboquant_kv/packed_attention.py:
+// 260-334 (tiled online softmax), split merge :328-334.
+#include "wtq_decode.cuh"
+
+namespace wtq {
+
+namespace mma4 {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kTileTokens = 16;
+constexpr int kTilesPerIter = 4;                       // 64 tokens per iteration
+constexpr int kIterTokens = kTileTokens * kTilesPerIter;
+constexpr int kVRow = 80;                              // padded value row (bank spread)
+constexpr int kOffV = 1024;                            // tile slot: K | V | nK | nV
+constexpr int kOffNK = kOffV + kTileTokens * kVRow;    // 2304
+constexpr int kOffNV = kOffNK + 32;                    // 2336
+constexpr int kSlot = kOffNV + 32;                     // 2368 bytes
+constexpr int kRing = 2 * kTilesPerIter * kSlot;       // two iterations per warp
+constexpr uint32_t kLutAddr = 0x10000;                 // shared address of the table
+constexpr uint32_t kLutBytes = 0x10000;
+constexpr float kPreciseAbove = 8.0f;                  // |score| (log2 units) that triggers fp32 rescoring
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float lds_half(uint32_t a) {
+  unsigned short h;
+  asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(h) : "r"(a));
+  return __half2float(__ushort_as_half(h));
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+// Table lookup of byte `K` (0..3) of `word`: `lane_sel` carries 0x10000, the
+// table bit and the lane's bank.
+template <int K> __device__ __forceinline__ uint32_t lut(uint32_t word, uint32_t lane_sel) {
+  return lds32(__byte_perm(word, lane_sel, 0x7604 | (K << 4)));
+}
+
+}  // namespace mma4
+
+using namespace mma4;
+
+// Rings live at fixed shared addresses: as many as fit between kRingLow and the
+// table, the rest after the table.  Dynamic shared memory starts at a small
+// driver-defined address (checked in the kernel to be <= kRingLow).
+constexpr uint32_t kRingLow = 2048;
+constexpr int kRingsBelow = (int)((kLutAddr - kRingLow) / kRing);
+constexpr int kRingsAbove = kWarps > kRingsBelow ? kWarps - kRingsBelow : 0;
+constexpr size_t kDynamicSmem = kLutAddr + kLutBytes + (size_t)kRingsAbove * kRing;
+static_assert(kDynamicSmem <= 227 * 1024, "shared memory budget");
+
+__device__ __forceinline__ uint32_t ring_address(int w) {
+  return w < kRingsBelow ? kRingLow + (uint32_t)w * kRing
+                         : kLutAddr + kLutBytes + (uint32_t)(w - kRingsBelow) * kRing;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p, int chunk_tokens) {
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(dyn_smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  if (dyn_base > kRingLow) {             // layout assumption broken: refuse, do not touch memory
+    if (p.status && tid == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+    return;
+  }
+
+  // ---- byte -> half2 tables, one copy per lane: [byte][K|V][lane] -----------
+  for (int e = tid; e < 256 * 64; e += kThreads) {
+    const int byte = e >> 6, side = (e >> 5) & 1;
+    const float *cent = side ? p.v.centroids : p.k.centroids;
+    sts32(kLutAddr + (uint32_t)e * 4u, pack_half2(cent[byte & 15], cent[byte >> 4]));
+  }
+  __syncthreads();
+
+  const uint32_t ring = ring_address(warp);
+  const uint32_t sel_k = 0x10000u | (uint32_t)(lane << 2);
+  const uint32_t sel_v = sel_k | 0x80u;
+  const int S = p.S;
+  const int chunks = p.num_splits;
+  const int64_t items = (int64_t)p.B * p.Hkv * chunks;
+  const int workers = gridDim.x * kWarps;
+
+  for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < items; item += workers) {
+    const int chunk = (int)(item % chunks);
+    const int kvh = (int)((item / chunks) % p.Hkv);
+    const int b = (int)(item / ((int64_t)chunks * p.Hkv));
+    int L = p.seq_lens[b];
+    if (L > p.max_pages * S) {
+      L = p.max_pages * S;
+      if (p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+    }
+    const int tok0 = chunk * chunk_tokens;
+    const int tok1 = min(L, tok0 + chunk_tokens);
+    if (tok0 >= tok1) continue;          // the merge only visits ceil(L / chunk) chunks
+
+    // ---- query fragments: head g, coordinates 32t .. 32t+31 ----------------
+    uint32_t qf[8][2];
+    {
+      const bool live = g < p.n_rep;
+      const float4 *src = reinterpret_cast<const float4 *>(
+          p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep + (live ? g : 0)) * 128 + 32 * t);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        float4 v = live ? src[ks] : make_float4(0.f, 0.f, 0.f, 0.f);
+        qf[ks][0] = pack_half2(v.x, v.y);
+        qf[ks][1] = pack_half2(v.z, v.w);
+      }
+    }
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const int n_iter = (tok1 - tok0 + kIterTokens - 1) / kIterTokens;
+    const uint8_t *k_head = p.k.pages + (int64_t)kvh * p.k.head_stride;
+    const uint8_t *v_head = p.v.pages + (int64_t)kvh * p.v.head_stride;
+    const __half *nk_head = p.k.norms + (int64_t)kvh * p.k.norm_head_stride;
+    const __half *nv_head = p.v.norms + (int64_t)kvh * p.v.norm_head_stride;
+    const int32_t *table = p.page_table + (int64_t)b * p.table_stride;
+
+    // Copies of one iteration (4 tiles) into half `buf` of the ring.  Lane l
+    // moves key chunks l and l+32 (exactly the 32 bytes it reads back itself),
+    // the same chunks of the values into padded rows, and lanes 0..3 the norms.
+    auto issue = [&](int it, int buf) {
+      if (it < n_iter) {
+#pragma unroll
+        for (int u = 0; u < kTilesPerIter; ++u) {
+          const int tok = tok0 + it * kIterTokens + u * kTileTokens;
+          if (tok < tok1) {
+            const int slot_page = tok / S;
+            const int sub = tok - slot_page * S;               // first slot of the tile
+            const int pid = table[slot_page];
+            if (pid >= 0 && pid < p.P) {
+              const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
+              const uint8_t *ks = k_head + (int64_t)pid * p.k.page_stride + sub * 64;
+              const uint8_t *vs = v_head + (int64_t)pid * p.v.page_stride + sub * 64;
+              cp_async16(dst + lane * 16, ks + lane * 16);
+              cp_async16(dst + 512 + lane * 16, ks + 512 + lane * 16);
+              cp_async16(dst + kOffV + g * kVRow + t * 16, vs + lane * 16);
+              cp_async16(dst + kOffV + (g + 8) * kVRow + t * 16, vs + 512 + lane * 16);
+              if (lane < 2)
+                cp_async16(dst + kOffNK + lane * 16,
+                           nk_head + (int64_t)pid * p.k.norm_page_stride + sub + lane * 8);
+              else if (lane < 4)
+                cp_async16(dst + kOffNV + (lane - 2) * 16,
+                           nv_head + (int64_t)pid * p.v.norm_page_stride + sub + (lane - 2) * 8);
+            } else if (p.status && lane == 0) {
+              atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+            }
+          }
+        }
+      }
+      cp_async_commit();
+    };
+
+    issue(0, 0);
+    for (int it = 0; it < n_iter; ++it) {
+      const int buf = it & 1;
+      issue(it + 1, buf ^ 1);
+      cp_async_wait<1>();
+      __syncwarp();
+
+      // ---- scores of the 4 tiles ------------------------------------------
+      float s[kTilesPerIter][4];
+      bool ok[kTilesPerIter][2];
+#pragma unroll
+      for (int u = 0; u < kTilesPerIter; ++u) {
+        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
+        const int tok = tok0 + it * kIterTokens + u * kTileTokens;
+        int pid = -1;
+        if (tok < tok1) pid = table[tok / S];
+        const bool page_ok = pid >= 0 && pid < p.P;
+        ok[u][0] = page_ok && tok + g < tok1;
+        ok[u][1] = page_ok && tok + g + 8 < tok1;
+        const uint4 r0 = lds128(slot + g * 64 + t * 16);
+        const uint4 r1 = lds128(slot + (g + 8) * 64 + t * 16);
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
+        const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mma16816(c, lut<0>(w0[j], sel_k), lut<0>(w1[j], sel_k), lut<1>(w0[j], sel_k),
+                   lut<1>(w1[j], sel_k), qf[2 * j][0], qf[2 * j][1]);
+          mma16816(c, lut<2>(w0[j], sel_k), lut<2>(w1[j], sel_k), lut<3>(w0[j], sel_k),
+                   lut<3>(w1[j], sel_k), qf[2 * j + 1][0], qf[2 * j + 1][1]);
+        }
+        const float nk0 = lds_half(slot + kOffNK + g * 2);
+        const float nk1 = lds_half(slot + kOffNK + (g + 8) * 2);
+        s[u][0] = ok[u][0] ? c[0] * nk0 : -INFINITY;
+        s[u][1] = ok[u][0] ? c[1] * nk0 : -INFINITY;
+        s[u][2] = ok[u][1] ? c[2] * nk1 : -INFINITY;
+        s[u][3] = ok[u][1] ? c[3] * nk1 : -INFINITY;
+      }
+
+      // ---- fp16 operands carry about 2^-11.5 of the score scale as error; when
+      // any score of these 64 tokens is large (|s| > 8 in log2 units) the tiles
+      // are scored again in fp32 on the CUDA cores, so that large logits cost
+      // time, not accuracy.
+      {
+        float big = 0.f;
+#pragma unroll
+        for (int u = 0; u < kTilesPerIter; ++u)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (s[u][e] != -INFINITY) big = fmaxf(big, fabsf(s[u][e]));
+        if (__any_sync(0xffffffffu, big > kPreciseAbove)) {
+          const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
+          const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
+          const float *qa = q0 + (h0 ? 2 * t : 0) * 128, *qb = q0 + (h1 ? 2 * t + 1 : 0) * 128;
+#pragma unroll
+          for (int u = 0; u < kTilesPerIter; ++u) {
+            const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 1
+            for (int w = 0; w < 16; ++w) {                 // 16 words of 8 codes per row
+              uint32_t x0 = lds32(slot + g * 64 + w * 4), x1 = lds32(slot + (g + 8) * 64 + w * 4);
+#pragma unroll
+              for (int n = 0; n < 8; ++n) {
+                const float c0 = __ldg(p.k.centroids + (x0 & 15u));
+                const float c1 = __ldg(p.k.centroids + (x1 & 15u));
+                const float fa = __ldg(qa + w * 8 + n), fb = __ldg(qb + w * 8 + n);
+                d0 = fmaf(fa, c0, d0); d1 = fmaf(fb, c0, d1);
+                d2 = fmaf(fa, c1, d2); d3 = fmaf(fb, c1, d3);
+                x0 >>= 4; x1 >>= 4;
+              }
+            }
+            const float nk0 = lds_half(slot + kOffNK + g * 2);
+            const float nk1 = lds_half(slot + kOffNK + (g + 8) * 2);
+            s[u][0] = ok[u][0] && h0 ? d0 * nk0 : (ok[u][0] ? 0.f : -INFINITY);
+            s[u][1] = ok[u][0] && h1 ? d1 * nk0 : (ok[u][0] ? 0.f : -INFINITY);
+            s[u][2] = ok[u][1] && h0 ? d2 * nk1 : (ok[u][1] ? 0.f : -INFINITY);
+            s[u][3] = ok[u][1] && h1 ? d3 * nk1 : (ok[u][1] ? 0.f : -INFINITY);
+          }
+        }
+      }
+
+      // ---- running max per head (heads 2t, 2t+1), shared over the 8 rows ----
+      float mx[2] = {m_run[0], m_run[1]};
+#pragma unroll
+      for (int u = 0; u < kTilesPerIter; ++u) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[u][0], s[u][2]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[u][1], s[u][3]));
+      }
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+      }
+      // exp2(-inf - -inf) is defined as 0: with nothing seen the base is 0
+      const float base0 = mx[0] == -INFINITY ? 0.f : mx[0];
+      const float base1 = mx[1] == -INFINITY ? 0.f : mx[1];
+      const float alpha0 = ex2(m_run[0] - base0), alpha1 = ex2(m_run[1] - base1);
+      if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc[j][0] *= alpha0; acc[j][1] *= alpha1; acc[j][2] *= alpha0; acc[j][3] *= alpha1;
+        }
+        l_run[0] *= alpha0;
+        l_run[1] *= alpha1;
+      }
+      m_run[0] = mx[0];
+      m_run[1] = mx[1];
+
+      // ---- values of the 4 tiles ------------------------------------------
+#pragma unroll
+      for (int u = 0; u < kTilesPerIter; ++u) {
+        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
+        const float nv0 = lds_half(slot + kOffNV + g * 2);
+        const float nv1 = lds_half(slot + kOffNV + (g + 8) * 2);
+        const float p0 = ex2(s[u][0] - base0), p1 = ex2(s[u][1] - base1);
+        const float p2 = ex2(s[u][2] - base0), p3 = ex2(s[u][3] - base1);
+        l_run[0] += p0 + p2;
+        l_run[1] += p1 + p3;
+        // rows g / g+8 of P' (token x head) -> B fragment (token pairs of head g)
+        const uint32_t pb0 = movmatrix_trans(
+            ok[u][0] ? pack_half2(p0 * nv0, p1 * nv0) : 0u);
+        const uint32_t pb1 = movmatrix_trans(
+            ok[u][1] ? pack_half2(p2 * nv1, p3 * nv1) : 0u);
+        const uint32_t vb = slot + kOffV + g * 8;
+        const uint2 wa = lds64(vb + (2 * t) * kVRow), wb = lds64(vb + (2 * t + 1) * kVRow);
+        const uint2 wc = lds64(vb + (2 * t + 8) * kVRow), wd = lds64(vb + (2 * t + 9) * kVRow);
+        // byte j of lo_* : low nibbles of tokens (A | B << 4) at coordinate 16g+2j
+        // byte j of hi_* : high nibbles, coordinate 16g+2j+1
+        const uint32_t lo_ab[2] = {(wa.x & 0x0F0F0F0Fu) | ((wb.x << 4) & 0xF0F0F0F0u),
+                                   (wa.y & 0x0F0F0F0Fu) | ((wb.y << 4) & 0xF0F0F0F0u)};
+        const uint32_t hi_ab[2] = {((wa.x >> 4) & 0x0F0F0F0Fu) | (wb.x & 0xF0F0F0F0u),
+                                   ((wa.y >> 4) & 0x0F0F0F0Fu) | (wb.y & 0xF0F0F0F0u)};
+        const uint32_t lo_cd[2] = {(wc.x & 0x0F0F0F0Fu) | ((wd.x << 4) & 0xF0F0F0F0u),
+                                   (wc.y & 0x0F0F0F0Fu) | ((wd.y << 4) & 0xF0F0F0F0u)};
+        const uint32_t hi_cd[2] = {((wc.x >> 4) & 0x0F0F0F0Fu) | (wd.x & 0xF0F0F0F0u),
+                                   ((wc.y >> 4) & 0x0F0F0F0Fu) | (wd.y & 0xF0F0F0F0u)};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mma16816(acc[4 * h + 0], lut<0>(lo_ab[h], sel_v), lut<0>(hi_ab[h], sel_v),
+                   lut<0>(lo_cd[h], sel_v), lut<0>(hi_cd[h], sel_v), pb0, pb1);
+          mma16816(acc[4 * h + 1], lut<1>(lo_ab[h], sel_v), lut<1>(hi_ab[h], sel_v),
+                   lut<1>(lo_cd[h], sel_v), lut<1>(hi_cd[h], sel_v), pb0, pb1);
+          mma16816(acc[4 * h + 2], lut<2>(lo_ab[h], sel_v), lut<2>(hi_ab[h], sel_v),
+                   lut<2>(lo_cd[h], sel_v), lut<2>(hi_cd[h], sel_v), pb0, pb1);
+          mma16816(acc[4 * h + 3], lut<3>(lo_ab[h], sel_v), lut<3>(hi_ab[h], sel_v),
+                   lut<3>(lo_cd[h], sel_v), lut<3>(hi_cd[h], sel_v), pb0, pb1);
+        }
+      }
+      __syncwarp();       // every lane is done with this half before it is refilled
+    }
+    cp_async_wait<0>();
+
+    // ---- partial state of this chunk ---------------------------------------
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
+      l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int h = 2 * t + e;
+      if (h < p.n_rep) {
+        const int64_t row = ((int64_t)b * p.Hq + kvh * p.n_rep + h) * chunks + chunk;
+        float2 *dst = reinterpret_cast<float2 *>(p.part_acc + row * 128 + 16 * g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j] = make_float2(acc[j][e], acc[j][2 + e]);
+        if (g == 0) {
+          p.part_m[row] = m_run[e];
+          p.part_l[row] = l_run[e];
+        }
+      }
+    }
+  }
+}
+
+// Merge of the chunk states of one (sequence, kv head) group and rotation of
+// its n_rep output rows back to the model basis: out = (sum_c w_c acc_c / sum_c
+// w_c l_c) Pi_V with w_c = 2^(m_c - max m).  Only the chunks that exist for
+// the sequence's length are read.  512 threads: warp w first merges head
+// w % n_rep ... (one warp per (head, quarter of the coordinates)); then thread
+// (c, part) accumulates output column c over a quarter of the rows of Pi_V for
+// every head of the group, and the four quarters are added through shared
+// memory.
+constexpr int kMergeThreads = 512;
+__global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
+    MergeParams p, const int32_t *seq_lens, int Hkv, int n_rep, int chunk_tokens, int max_tokens) {
+  __shared__ float a_s[8][128];
+  __shared__ float w_s[8][kMaxSplits];
+  __shared__ float inv_s[8];
+  __shared__ float o_s[4][8][128];
+  const int b = blockIdx.x / Hkv, kvh = blockIdx.x - b * Hkv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int L = seq_lens[b];
+  L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
+  const int chunks = (L + chunk_tokens - 1) / chunk_tokens;
+  const int64_t row0 = ((int64_t)b * p.Hq + kvh * n_rep) * p.num_splits;
+  if (warp < n_rep) {                                  // weights of head `warp`
+    const int64_t base = row0 + (int64_t)warp * p.num_splits;
+    float gmax = -INFINITY;
+    for (int c = lane; c < chunks; c += 32) gmax = fmaxf(gmax, p.part_m[base + c]);
+    gmax = warp_max(gmax);
+    float denom = 0.f;
+    for (int c = lane; c < chunks; c += 32) {
+      const float m = p.part_m[base + c];
+      const float w = m == -INFINITY ? 0.f : exp2f(m - gmax);
+      w_s[warp][c] = w;
+      denom += w * p.part_l[base + c];
+    }
+    denom = warp_sum(denom);
+    if (lane == 0) inv_s[warp] = denom > 0.f ? 1.f / fmaxf(denom, 1e-30f) : 0.f;
+  }
+  __syncthreads();
+  for (int e = tid; e < n_rep * 128; e += kMergeThreads) {
+    const int h = e >> 7, d = e & 127;
+    const float *src = p.part_acc + (row0 + (int64_t)h * p.num_splits) * 128 + d;
+    float a = 0.f;
+#pragma unroll 4
+    for (int c = 0; c < chunks; ++c) a = fmaf(w_s[h][c], src[(int64_t)c * 128], a);
+    a_s[h][d] = a * inv_s[h];
+  }
+  __syncthreads();
+  const int col = tid & 127, part = tid >> 7;
+  float o[8];
+#pragma unroll
+  for (int h = 0; h < 8; ++h) o[h] = 0.f;
+#pragma unroll 8
+  for (int d = part * 32; d < part * 32 + 32; ++d) {
+    const float w = __ldg(p.Pi_v + d * 128 + col);
+#pragma unroll
+    for (int h = 0; h < 8; ++h) o[h] = fmaf(a_s[h][d], w, o[h]);
+  }
+#pragma unroll
+  for (int h = 0; h < 8; ++h) o_s[part][h][col] = o[h];
+  __syncthreads();
+  for (int e = tid; e < n_rep * 128; e += kMergeThreads) {
+    const int h = e >> 7, c = e & 127;
+    const float v = (o_s[0][h][c] + o_s[1][h][c]) + (o_s[2][h][c] + o_s[3][h][c]);
+    store_from_float(p.out, (int64_t)b * p.osb + (int64_t)(kvh * n_rep + h) * p.osh + c, v, p.dtype);
+  }
+}
+
+bool mma4_eligible(const DecodeParams &p) {
+  auto aligned = [](const void *ptr) { return ((uintptr_t)ptr & 15) == 0; };
+  return p.D == 128 && p.k.bw == 4 && p.v.bw == 4 && p.S % 16 == 0 && p.n_rep <= 8 &&
+         aligned(p.k.pages) && aligned(p.v.pages) && aligned(p.k.norms) && aligned(p.v.norms) &&
+         p.k.page_stride % 16 == 0 && p.k.head_stride % 16 == 0 && p.v.page_stride % 16 == 0 &&
+         p.v.head_stride % 16 == 0 && p.k.norm_page_stride % 8 == 0 &&
+         p.k.norm_head_stride % 8 == 0 && p.v.norm_page_stride % 8 == 0 &&
+         p.v.norm_head_stride % 8 == 0 && aligned(p.q_rot) && aligned(p.part_acc);
+}
+
+// Tokens per chunk for `splits` chunks over `max_tokens`, a multiple of 64.
+int mma4_chunk_tokens(int max_tokens, int splits) {
+  int per = (max_tokens + splits - 1) / splits;
+  per = (per + kIterTokens - 1) / kIterTokens * kIterTokens;
+  return per < kIterTokens ? kIterTokens : per;
+}
+
+int launch_decode_mma4(const DecodeParams &p, const MergeParams &m, cudaStream_t stream) {
+  static int sms = 0;
+  const size_t smem = kDynamicSmem;
+  if (sms == 0) {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(decode_mma4_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return check_cuda(e, "wtq_decode: shared memory opt-in");
+    sms = n > 0 ? n : 148;
+  }
+  const int max_tokens = p.max_pages * p.S;
+  const int chunk_tokens = mma4_chunk_tokens(max_tokens, p.num_splits);
+  const int64_t items = (int64_t)p.B * p.Hkv * p.num_splits;
+  int grid = (int)((items + kWarps - 1) / kWarps);
+  if (grid > sms) grid = sms;
+  profile_mark_begin(stream);
+  decode_mma4_kernel<<<grid, kThreads, smem, stream>>>(p, chunk_tokens);
+  profile_mark_end(stream);
+  if (int rc = check_cuda(cudaGetLastError(), "wtq_decode mma launch")) return rc;
+  merge_group_kernel<<<p.B * p.Hkv, kMergeThreads, 0, stream>>>(m, p.seq_lens, p.Hkv, p.n_rep, chunk_tokens,
+                                                     max_tokens);
+  note_launches(2);
+  return check_cuda(cudaGetLastError(), "wtq_decode merge launch");
+}
+
+}  // namespace wtq
