@@ -63,11 +63,11 @@ extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pag
   if (B < 1 || Hkv < 1 || Hq < 1) return 1;
   const int64_t groups = (int64_t)B * Hkv;
   const int64_t max_tokens = (int64_t)max_pages * S;
-  if (D == 128 && bw_k == 4 && bw_v == 4 && S % 16 == 0 && Hq / Hkv <= 8) {
-    // tensor-core path: every warp of the persistent grid (8 per SM) should see
+  if (D == 128 && bw_k == 4 && bw_v == 4 && S >= 16 && (S & (S - 1)) == 0 && Hq / Hkv <= 8) {
+    // tensor-core path: every warp of the persistent grid (16 per SM) should see
     // about three chunks, and a chunk should be long enough (>= 256 tokens)
     // that writing its partial state stays small beside reading its pages
-    const int64_t workers = (int64_t)device_sms() * 8;
+    const int64_t workers = (int64_t)device_sms() * 16;
     int64_t chunk = (max_tokens * groups + 3 * workers - 1) / (3 * workers);
     chunk = (chunk + 63) / 64 * 64;
     if (chunk < 256) chunk = 256;

@@ -17,20 +17,61 @@
 
 namespace wtq {
 
-__global__ void rotate_q_kernel(const void *q, int dtype, int64_t qsb, int64_t qsh,
-                                const float *Pi, float scale, int Hq, int D, float *q_rot) {
-  __shared__ float qs[256];
-  const int row = blockIdx.x;
-  const int b = row / Hq, h = row - b * Hq;
-  for (int d = threadIdx.x; d < D; d += blockDim.x)
-    qs[d] = load_as_float(q, (int64_t)b * qsb + (int64_t)h * qsh + d, dtype);
+// q_rot[row][c] = mult * sum_d q[row][d] Pi[c][d] for the `rows` query rows that
+// start at row blockIdx.x * NR.  A warp takes output coordinates c = warp,
+// warp + 16, ...; its lanes stride over d, so every Pi row is read once per
+// block, coalesced, for all NR query rows, and the NR partial sums are reduced
+// by shuffles.  Eight Pi rows are in flight per warp to cover L2 latency.
+constexpr int kRotThreads = 512;
+template <int NR>
+__global__ void __launch_bounds__(kRotThreads) rotate_q_kernel(
+    const void *q, int dtype, int64_t qsb, int64_t qsh, const float *Pi, float mult, int Hq,
+    int D, int total_rows, float *q_rot) {
+  __shared__ float qs[NR][256];
+  const int row0 = blockIdx.x * NR;
+  for (int e = threadIdx.x; e < NR * D; e += kRotThreads) {
+    const int r = e / D, d = e - r * D;
+    const int row = row0 + r;
+    float v = 0.f;
+    if (row < total_rows) {
+      const int b = row / Hq, h = row - b * Hq;
+      v = load_as_float(q, (int64_t)b * qsb + (int64_t)h * qsh + d, dtype);
+    }
+    qs[r][d] = v;
+  }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int c = warp; c < D; c += warps) {
-    float part = 0.0f;
-    for (int d = lane; d < D; d += 32) part = fmaf(qs[d], Pi[(int64_t)c * D + d], part);
-    part = warp_sum(part);
-    if (lane == 0) q_rot[(int64_t)row * D + c] = part * scale;
+  // the page scan that follows may start its own prologue now
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kWarps = kRotThreads / 32, kBatch = 8;
+  for (int c0 = warp; c0 < D; c0 += kWarps * kBatch) {
+    float part[kBatch][NR];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+      for (int r = 0; r < NR; ++r) part[i][r] = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      float w[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const int c = c0 + i * kWarps;
+        w[i] = c < D ? __ldg(Pi + (int64_t)c * D + d) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+        for (int r = 0; r < NR; ++r) part[i][r] = fmaf(qs[r][d], w[i], part[i][r]);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int c = c0 + i * kWarps;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const float v = warp_sum(part[i][r]);
+        if (lane == 0 && c < D && row0 + r < total_rows)
+          q_rot[(int64_t)(row0 + r) * D + c] = v * mult;
+      }
+    }
   }
 }
 
@@ -272,7 +313,13 @@ int launch_decode_generic(const DecodeParams &p, cudaStream_t stream) {
 
 int launch_rotate_q(const void *q, int dtype, const int64_t *qs, const float *Pi, float scale,
                     int B, int Hq, int D, float *q_rot, cudaStream_t stream) {
-  rotate_q_kernel<<<B * Hq, 128, 0, stream>>>(q, dtype, qs[0], qs[1], Pi, scale, Hq, D, q_rot);
+  const int rows = B * Hq;
+  if (rows % 4 == 0)
+    rotate_q_kernel<4><<<rows / 4, kRotThreads, 0, stream>>>(q, dtype, qs[0], qs[1], Pi, scale, Hq,
+                                                            D, rows, q_rot);
+  else
+    rotate_q_kernel<1><<<rows, kRotThreads, 0, stream>>>(q, dtype, qs[0], qs[1], Pi, scale, Hq, D,
+                                                        rows, q_rot);
   note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_decode rotate launch");
 }

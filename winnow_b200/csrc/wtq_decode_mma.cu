@@ -1,12 +1,12 @@
 // Split-K decode attention over paged packed K/V: the sm_100a fast path for
-// head_dim 128, 4-bit keys and values, pages of a multiple of 16 tokens and a
+// head_dim 128, 4-bit keys and values, pages of 16, 32, 64, ... tokens and a
 // GQA group of at most 8 query heads.
 //
-// One persistent CTA per SM, 8 warps.  A warp is an independent worker: it
+// One persistent CTA per SM, 16 warps.  A warp is an independent worker: it
 // takes (sequence, kv head, chunk of tokens) items round-robin, streams the
 // chunk's 16-token tiles from HBM into its private shared-memory ring with
-// 16-byte cp.async copies (the next 64 tokens are in flight while the current
-// 64 are consumed), and keeps the whole flash-decoding state in registers.
+// 16-byte cp.async copies (the next 32 tokens are in flight while the current
+// 32 are consumed), and keeps the whole flash-decoding state in registers.
 //
 // Per 16-token tile, with the packed bytes never leaving registers/smem:
 //   scores   S^T[16 tok x 8 heads] = C_K[16 x 128] . Qrot^T   8 x mma.m16n8k16
@@ -36,10 +36,10 @@ namespace wtq {
 
 namespace mma4 {
 
-constexpr int kWarps = 8;
+constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kTileTokens = 16;
-constexpr int kTilesPerIter = 4;                       // 64 tokens per iteration
+constexpr int kTilesPerIter = 2;                       // 32 tokens per iteration
 constexpr int kIterTokens = kTileTokens * kTilesPerIter;
 constexpr int kVRow = 80;                              // padded value row (bank spread)
 constexpr int kOffV = 1024;                            // tile slot: K | V | nK | nV
@@ -130,6 +130,30 @@ __device__ __forceinline__ uint32_t ring_address(int w) {
                          : kLutAddr + kLutBytes + (uint32_t)(w - kRingsBelow) * kRing;
 }
 
+// fp32 scores of tile rows g and g+8 against two query rows (already rotated
+// and scaled, read through L1), times the key norms: {row g . qa, row g . qb,
+// row g+8 . qa, row g+8 . qb}.  Kept out of line: it runs only for windows
+// whose fp16 scores came out large, and must not cost the common path
+// registers.
+__device__ __noinline__ float4 precise_scores(uint32_t slot, int g, const float *qa,
+                                              const float *qb, const float *centroids) {
+  float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll 1
+  for (int w = 0; w < 16; ++w) {                       // 16 words of 8 codes per row
+    uint32_t x0 = lds32(slot + g * 64 + w * 4), x1 = lds32(slot + (g + 8) * 64 + w * 4);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const float c0 = __ldg(centroids + (x0 & 15u)), c1 = __ldg(centroids + (x1 & 15u));
+      const float fa = __ldg(qa + w * 8 + n), fb = __ldg(qb + w * 8 + n);
+      d0 = fmaf(fa, c0, d0); d1 = fmaf(fb, c0, d1);
+      d2 = fmaf(fa, c1, d2); d3 = fmaf(fb, c1, d3);
+      x0 >>= 4; x1 >>= 4;
+    }
+  }
+  const float nk0 = lds_half(slot + kOffNK + g * 2), nk1 = lds_half(slot + kOffNK + (g + 8) * 2);
+  return make_float4(d0 * nk0, d1 * nk0, d2 * nk1, d3 * nk1);
+}
+
 __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p, int chunk_tokens) {
   extern __shared__ __align__(16) uint8_t dyn_smem[];
   const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(dyn_smem);
@@ -152,11 +176,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
   const uint32_t sel_k = 0x10000u | (uint32_t)(lane << 2);
   const uint32_t sel_v = sel_k | 0x80u;
   const int S = p.S;
+  const int s_shift = 31 - __clz(S);                 // S is a power of two (checked by the host)
+  const uint32_t v_dst = (uint32_t)(g * kVRow + t * 16);
   const int chunks = p.num_splits;
   const int64_t items = (int64_t)p.B * p.Hkv * chunks;
   const int workers = gridDim.x * kWarps;
 
-  for (int64_t item = (int64_t)blockIdx.x * kWarps + warp; item < items; item += workers) {
+  // q_rot is written by the kernel launched just before this one; everything
+  // above overlapped with its tail.  The merge that follows may be scheduled as
+  // soon as SMs free up.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
+  // Consecutive items go to different CTAs, so a last, partly filled round of
+  // items is spread over all SMs instead of filling a few of them.
+  for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; item < items; item += workers) {
     const int chunk = (int)(item % chunks);
     const int kvh = (int)((item / chunks) % p.Hkv);
     const int b = (int)(item / ((int64_t)chunks * p.Hkv));
@@ -197,23 +231,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
     // Copies of one iteration (4 tiles) into half `buf` of the ring.  Lane l
     // moves key chunks l and l+32 (exactly the 32 bytes it reads back itself),
     // the same chunks of the values into padded rows, and lanes 0..3 the norms.
-    auto issue = [&](int it, int buf) {
+    // Returns a bit per tile: set when the tile's page id was inside the pool
+    // and its copies were issued.
+    auto issue = [&](int it, int buf) -> uint32_t {
+      uint32_t loaded = 0;
       if (it < n_iter) {
 #pragma unroll
         for (int u = 0; u < kTilesPerIter; ++u) {
           const int tok = tok0 + it * kIterTokens + u * kTileTokens;
           if (tok < tok1) {
-            const int slot_page = tok / S;
-            const int sub = tok - slot_page * S;               // first slot of the tile
-            const int pid = table[slot_page];
+            const int sub = tok & (S - 1);                     // first slot of the tile
+            const int pid = table[tok >> s_shift];
             if (pid >= 0 && pid < p.P) {
+              loaded |= 1u << u;
               const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
-              const uint8_t *ks = k_head + (int64_t)pid * p.k.page_stride + sub * 64;
-              const uint8_t *vs = v_head + (int64_t)pid * p.v.page_stride + sub * 64;
-              cp_async16(dst + lane * 16, ks + lane * 16);
-              cp_async16(dst + 512 + lane * 16, ks + 512 + lane * 16);
-              cp_async16(dst + kOffV + g * kVRow + t * 16, vs + lane * 16);
-              cp_async16(dst + kOffV + (g + 8) * kVRow + t * 16, vs + 512 + lane * 16);
+              const uint8_t *ks = k_head + (int64_t)pid * p.k.page_stride + (sub * 64 + lane * 16);
+              const uint8_t *vs = v_head + (int64_t)pid * p.v.page_stride + (sub * 64 + lane * 16);
+              cp_async16(dst + lane * 16, ks);
+              cp_async16(dst + 512 + lane * 16, ks + 512);
+              cp_async16(dst + kOffV + v_dst, vs);
+              cp_async16(dst + kOffV + 8 * kVRow + v_dst, vs + 512);
               if (lane < 2)
                 cp_async16(dst + kOffNK + lane * 16,
                            nk_head + (int64_t)pid * p.k.norm_page_stride + sub + lane * 8);
@@ -227,25 +264,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
         }
       }
       cp_async_commit();
+      return loaded;
     };
 
-    issue(0, 0);
+    uint32_t loaded_next = issue(0, 0);
     for (int it = 0; it < n_iter; ++it) {
       const int buf = it & 1;
-      issue(it + 1, buf ^ 1);
+      const uint32_t loaded = loaded_next;
+      loaded_next = issue(it + 1, buf ^ 1);
       cp_async_wait<1>();
       __syncwarp();
 
       // ---- scores of the 4 tiles ------------------------------------------
       float s[kTilesPerIter][4];
       bool ok[kTilesPerIter][2];
+      float big = 0.f;
 #pragma unroll
       for (int u = 0; u < kTilesPerIter; ++u) {
         const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
         const int tok = tok0 + it * kIterTokens + u * kTileTokens;
-        int pid = -1;
-        if (tok < tok1) pid = table[tok / S];
-        const bool page_ok = pid >= 0 && pid < p.P;
+        const bool page_ok = (loaded >> u) & 1u;
         ok[u][0] = page_ok && tok + g < tok1;
         ok[u][1] = page_ok && tok + g + 8 < tok1;
         const uint4 r0 = lds128(slot + g * 64 + t * 16);
@@ -262,23 +300,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
         }
         const float nk0 = lds_half(slot + kOffNK + g * 2);
         const float nk1 = lds_half(slot + kOffNK + (g + 8) * 2);
-        s[u][0] = ok[u][0] ? c[0] * nk0 : -INFINITY;
-        s[u][1] = ok[u][0] ? c[1] * nk0 : -INFINITY;
-        s[u][2] = ok[u][1] ? c[2] * nk1 : -INFINITY;
-        s[u][3] = ok[u][1] ? c[3] * nk1 : -INFINITY;
+        c[0] *= nk0; c[1] *= nk0; c[2] *= nk1; c[3] *= nk1;
+        big = fmaxf(big, ok[u][0] ? fmaxf(fabsf(c[0]), fabsf(c[1])) : 0.f);
+        big = fmaxf(big, ok[u][1] ? fmaxf(fabsf(c[2]), fabsf(c[3])) : 0.f);
+        s[u][0] = ok[u][0] ? c[0] : -INFINITY;
+        s[u][1] = ok[u][0] ? c[1] : -INFINITY;
+        s[u][2] = ok[u][1] ? c[2] : -INFINITY;
+        s[u][3] = ok[u][1] ? c[3] : -INFINITY;
       }
 
       // ---- fp16 operands carry about 2^-11.5 of the score scale as error; when
-      // any score of these 64 tokens is large (|s| > 8 in log2 units) the tiles
-      // are scored again in fp32 on the CUDA cores, so that large logits cost
-      // time, not accuracy.
+      // any score of this window is large (|s| > 8 in log2 units) its tiles are
+      // scored again in fp32 on the CUDA cores, so that large logits cost time,
+      // not accuracy.
       {
-        float big = 0.f;
-#pragma unroll
-        for (int u = 0; u < kTilesPerIter; ++u)
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (s[u][e] != -INFINITY) big = fmaxf(big, fabsf(s[u][e]));
         if (__any_sync(0xffffffffu, big > kPreciseAbove)) {
           const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
           const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
@@ -286,26 +321,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
 #pragma unroll
           for (int u = 0; u < kTilesPerIter; ++u) {
             const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll 1
-            for (int w = 0; w < 16; ++w) {                 // 16 words of 8 codes per row
-              uint32_t x0 = lds32(slot + g * 64 + w * 4), x1 = lds32(slot + (g + 8) * 64 + w * 4);
-#pragma unroll
-              for (int n = 0; n < 8; ++n) {
-                const float c0 = __ldg(p.k.centroids + (x0 & 15u));
-                const float c1 = __ldg(p.k.centroids + (x1 & 15u));
-                const float fa = __ldg(qa + w * 8 + n), fb = __ldg(qb + w * 8 + n);
-                d0 = fmaf(fa, c0, d0); d1 = fmaf(fb, c0, d1);
-                d2 = fmaf(fa, c1, d2); d3 = fmaf(fb, c1, d3);
-                x0 >>= 4; x1 >>= 4;
-              }
-            }
-            const float nk0 = lds_half(slot + kOffNK + g * 2);
-            const float nk1 = lds_half(slot + kOffNK + (g + 8) * 2);
-            s[u][0] = ok[u][0] && h0 ? d0 * nk0 : (ok[u][0] ? 0.f : -INFINITY);
-            s[u][1] = ok[u][0] && h1 ? d1 * nk0 : (ok[u][0] ? 0.f : -INFINITY);
-            s[u][2] = ok[u][1] && h0 ? d2 * nk1 : (ok[u][1] ? 0.f : -INFINITY);
-            s[u][3] = ok[u][1] && h1 ? d3 * nk1 : (ok[u][1] ? 0.f : -INFINITY);
+            const float4 d = precise_scores(slot, g, qa, qb, p.k.centroids);
+            s[u][0] = ok[u][0] ? (h0 ? d.x : 0.f) : -INFINITY;
+            s[u][1] = ok[u][0] ? (h1 ? d.y : 0.f) : -INFINITY;
+            s[u][2] = ok[u][1] ? (h0 ? d.z : 0.f) : -INFINITY;
+            s[u][3] = ok[u][1] ? (h1 ? d.w : 0.f) : -INFINITY;
           }
         }
       }
@@ -421,6 +441,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
   __shared__ float o_s[4][8][128];
   const int b = blockIdx.x / Hkv, kvh = blockIdx.x - b * Hkv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");      // partial states are complete
   int L = seq_lens[b];
   L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
   const int chunks = (L + chunk_tokens - 1) / chunk_tokens;
@@ -445,8 +466,13 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
     const int h = e >> 7, d = e & 127;
     const float *src = p.part_acc + (row0 + (int64_t)h * p.num_splits) * 128 + d;
     float a = 0.f;
-#pragma unroll 4
-    for (int c = 0; c < chunks; ++c) a = fmaf(w_s[h][c], src[(int64_t)c * 128], a);
+    for (int c0 = 0; c0 < chunks; c0 += 16) {              // 16 loads in flight
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = c0 + i < chunks ? __ldcg(src + (int64_t)(c0 + i) * 128) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) a = fmaf(c0 + i < chunks ? w_s[h][c0 + i] : 0.f, v[i], a);
+    }
     a_s[h][d] = a * inv_s[h];
   }
   __syncthreads();
@@ -454,12 +480,13 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
   float o[8];
 #pragma unroll
   for (int h = 0; h < 8; ++h) o[h] = 0.f;
-#pragma unroll 8
-  for (int d = part * 32; d < part * 32 + 32; ++d) {
-    const float w = __ldg(p.Pi_v + d * 128 + col);
+  float wv[32];
 #pragma unroll
-    for (int h = 0; h < 8; ++h) o[h] = fmaf(a_s[h][d], w, o[h]);
-  }
+  for (int i = 0; i < 32; ++i) wv[i] = __ldg(p.Pi_v + (part * 32 + i) * 128 + col);
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+#pragma unroll
+    for (int h = 0; h < 8; ++h) o[h] = fmaf(a_s[h][part * 32 + i], wv[i], o[h]);
 #pragma unroll
   for (int h = 0; h < 8; ++h) o_s[part][h][col] = o[h];
   __syncthreads();
@@ -472,7 +499,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
 
 bool mma4_eligible(const DecodeParams &p) {
   auto aligned = [](const void *ptr) { return ((uintptr_t)ptr & 15) == 0; };
-  return p.D == 128 && p.k.bw == 4 && p.v.bw == 4 && p.S % 16 == 0 && p.n_rep <= 8 &&
+  return p.D == 128 && p.k.bw == 4 && p.v.bw == 4 && p.S >= 16 && (p.S & (p.S - 1)) == 0 && p.n_rep <= 8 &&
          aligned(p.k.pages) && aligned(p.v.pages) && aligned(p.k.norms) && aligned(p.v.norms) &&
          p.k.page_stride % 16 == 0 && p.k.head_stride % 16 == 0 && p.v.page_stride % 16 == 0 &&
          p.v.head_stride % 16 == 0 && p.k.norm_page_stride % 8 == 0 &&
@@ -504,14 +531,29 @@ int launch_decode_mma4(const DecodeParams &p, const MergeParams &m, cudaStream_t
   const int64_t items = (int64_t)p.B * p.Hkv * p.num_splits;
   int grid = (int)((items + kWarps - 1) / kWarps);
   if (grid > sms) grid = sms;
+  // Both launches may begin before the kernel ahead of them has drained; each
+  // kernel waits (griddepcontrol.wait) before it touches what that kernel wrote.
+  cudaLaunchAttribute pdl;
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
   profile_mark_begin(stream);
-  decode_mma4_kernel<<<grid, kThreads, smem, stream>>>(p, chunk_tokens);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma4_kernel, p, chunk_tokens);
   profile_mark_end(stream);
-  if (int rc = check_cuda(cudaGetLastError(), "wtq_decode mma launch")) return rc;
-  merge_group_kernel<<<p.B * p.Hkv, kMergeThreads, 0, stream>>>(m, p.seq_lens, p.Hkv, p.n_rep, chunk_tokens,
-                                                     max_tokens);
+  if (e != cudaSuccess) return check_cuda(e, "wtq_decode mma launch");
+  cfg.gridDim = dim3((unsigned)(p.B * p.Hkv));
+  cfg.blockDim = dim3(kMergeThreads);
+  cfg.dynamicSmemBytes = 0;
+  e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, p.seq_lens, p.Hkv, p.n_rep, chunk_tokens,
+                         max_tokens);
   note_launches(2);
-  return check_cuda(cudaGetLastError(), "wtq_decode merge launch");
+  return check_cuda(e, "wtq_decode merge launch");
 }
 
 }  // namespace wtq

@@ -58,6 +58,74 @@ def decode_workspace(B: int, Hq: int, Hkv: int, D: int, max_pages: int, S: int,
     return ws
 
 
+class DecodePlan:
+    """One decode call with every argument marshalled ahead of time.
+
+    A serving loop calls the operator with the same tensors step after step
+    (the page table, lengths, query and output buffers are updated in place),
+    so the contract checks and the ctypes marshalling are done once here and
+    `run()` is a single call into the library on the current stream.  The plan
+    keeps its tensors alive.  `graph()` captures the call's launches into a
+    CUDA graph for replay.
+    """
+
+    def __init__(self, q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
+                 num_splits: int | None = None, out: torch.Tensor | None = None,
+                 workspace: torch.Tensor | None = None, status: torch.Tensor | None = None,
+                 check_page_ids: bool = True):
+        check_kernel_contract(q, kv, check_page_ids=check_page_ids)
+        B, Hq, _, D = q.shape
+        dev = q.device
+        Hkv, S, P = kv.num_kv_heads, kv.page_size, kv.k_pages.shape[0]
+        max_pages = kv.page_table.shape[1]
+        if q.stride(-1) != 1:
+            raise pa.UnsupportedLayout("q must have unit stride in its last dimension")
+        if out is None:
+            out = torch.empty(B, Hq, 1, D, dtype=q.dtype, device=dev)
+        elif tuple(out.shape) != (B, Hq, 1, D) or out.dtype != q.dtype or out.stride(-1) != 1 \
+                or out.device != dev:
+            raise pa.UnsupportedLayout("out must be (B, Hq, 1, D) in q.dtype with unit stride in D")
+        self.out, self.device = out, dev
+        self.empty = B == 0 or max_pages == 0
+        if self.empty:
+            return
+        splits = int(num_splits or 0)
+        if workspace is None:
+            workspace = decode_workspace(B, Hq, Hkv, D, max_pages, S, splits, dev)
+        self._keep = (q, kv, out, workspace, status)
+        self._k_side = _side(kv.k_pages, kv.k_norms, kv.k_quant)
+        self._v_side = _side(kv.v_pages, kv.v_norms, kv.v_quant)
+        self._qs = _lib.i64x(q.stride(0), q.stride(1))
+        self._os = _lib.i64x(out.stride(0), out.stride(1))
+        self._fn = _lib.lib().wtq_decode
+        self._args = (
+            q.data_ptr(), _lib.dtype_code(q.dtype), self._qs, out.data_ptr(), self._os,
+            ctypes.byref(self._k_side), ctypes.byref(self._v_side),
+            kv.page_table.data_ptr(), kv.page_table.stride(0), kv.seq_lens.data_ptr(),
+            float(scale), B, Hq, Hkv, D, S, P, max_pages, splits,
+            workspace.data_ptr(), workspace.numel(),
+            status.data_ptr() if status is not None else None)
+
+    def run(self) -> torch.Tensor:
+        if self.empty:
+            return self.out.zero_() if self.out.numel() else self.out
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._fn(*self._args, stream)
+        if rc:
+            _lib.check(rc)
+        return self.out
+
+    def graph(self) -> "torch.cuda.CUDAGraph":
+        """The call captured as a CUDA graph (replay with `.replay()`)."""
+        with torch.cuda.device(self.device):
+            self.run()                                   # first call: one-time attribute set-up
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.run()
+        return g
+
+
 @torch.no_grad()
 def packed_decode_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
                             num_splits: int | None = None, allow_tf32: bool = False,
@@ -74,38 +142,13 @@ def packed_decode_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
     the CUDA schedule.  `out` may be a (B, Hq, 1, D) view into a larger buffer
     (e.g. this rank's heads inside a gathered output) with unit stride in D.
     """
-    check_kernel_contract(q, kv, check_page_ids=check_page_ids)
     if pages_per_iter < 1 or pages_per_iter & (pages_per_iter - 1):
+        pa.check_contract(q, kv, check_page_ids=False)
         raise pa.UnsupportedLayout("pages_per_iter must be a power of two >= 1")
     del allow_tf32, num_warps, num_stages
-    B, Hq, _, D = q.shape
-    dev = q.device
-    Hkv, S, P = kv.num_kv_heads, kv.page_size, kv.k_pages.shape[0]
-    max_pages = kv.page_table.shape[1]
-    if q.stride(-1) != 1:
+    if q.dim() == 4 and q.stride(-1) != 1:
         q = q.contiguous()
-    if out is None:
-        out = torch.empty(B, Hq, 1, D, dtype=q.dtype, device=dev)
-    elif tuple(out.shape) != (B, Hq, 1, D) or out.dtype != q.dtype or out.stride(-1) != 1 \
-            or out.device != dev:
-        raise pa.UnsupportedLayout("out must be (B, Hq, 1, D) in q.dtype with unit stride in D")
-    if B == 0:
-        return out
-    if max_pages == 0:
-        return out.zero_()
-    L = _lib.lib()
-    splits = int(num_splits or 0)
-    if workspace is None:
-        workspace = decode_workspace(B, Hq, Hkv, D, max_pages, S, splits, dev)
-    k_side = _side(kv.k_pages, kv.k_norms, kv.k_quant)
-    v_side = _side(kv.v_pages, kv.v_norms, kv.v_quant)
-    with torch.cuda.device(dev):
-        _lib.check(L.wtq_decode(
-            q.data_ptr(), _lib.dtype_code(q.dtype), _lib.i64x(q.stride(0), q.stride(1)),
-            out.data_ptr(), _lib.i64x(out.stride(0), out.stride(1)),
-            ctypes.byref(k_side), ctypes.byref(v_side),
-            kv.page_table.data_ptr(), kv.page_table.stride(0), kv.seq_lens.data_ptr(),
-            float(scale), B, Hq, Hkv, D, S, P, max_pages, splits,
-            workspace.data_ptr(), workspace.numel(),
-            status.data_ptr() if status is not None else None, _lib.stream_ptr(dev)))
-    return out
+    plan = DecodePlan(q, kv, scale, num_splits=num_splits, out=out, workspace=workspace,
+                      status=status, check_page_ids=check_page_ids)
+    with torch.cuda.device(q.device):
+        return plan.run()
