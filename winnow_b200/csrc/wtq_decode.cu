@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(kRotThreads) rotate_q_kernel(
     for (int i = 0; i < kBatch; ++i)
 #pragma unroll
       for (int r = 0; r < NR; ++r) part[i][r] = 0.f;
+#pragma unroll 4
     for (int d = lane; d < D; d += 32) {
       float w[kBatch];
 #pragma unroll

@@ -441,6 +441,12 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
   __shared__ float o_s[4][8][128];
   const int b = blockIdx.x / Hkv, kvh = blockIdx.x - b * Hkv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Pi_V does not depend on the scan: fetch this thread's 32 elements while the
+  // scan kernel is still draining.
+  const int col = tid & 127, part = tid >> 7;
+  float wv[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) wv[i] = __ldg(p.Pi_v + (part * 32 + i) * 128 + col);
   asm volatile("griddepcontrol.wait;\n" ::: "memory");      // partial states are complete
   int L = seq_lens[b];
   L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
@@ -448,15 +454,24 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
   const int64_t row0 = ((int64_t)b * p.Hq + kvh * n_rep) * p.num_splits;
   if (warp < n_rep) {                                  // weights of head `warp`
     const int64_t base = row0 + (int64_t)warp * p.num_splits;
-    float gmax = -INFINITY;
-    for (int c = lane; c < chunks; c += 32) gmax = fmaxf(gmax, p.part_m[base + c]);
+    // up to 8 chunks per lane (256 chunks at most), m and l fetched together
+    float mv[8], lv[8], gmax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      mv[i] = c < chunks ? __ldcg(p.part_m + base + c) : -INFINITY;
+      lv[i] = c < chunks ? __ldcg(p.part_l + base + c) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gmax = fmaxf(gmax, mv[i]);
     gmax = warp_max(gmax);
     float denom = 0.f;
-    for (int c = lane; c < chunks; c += 32) {
-      const float m = p.part_m[base + c];
-      const float w = m == -INFINITY ? 0.f : exp2f(m - gmax);
-      w_s[warp][c] = w;
-      denom += w * p.part_l[base + c];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      const float w = mv[i] == -INFINITY ? 0.f : exp2f(mv[i] - gmax);
+      if (c < chunks) w_s[warp][c] = w;
+      denom += w * lv[i];
     }
     denom = warp_sum(denom);
     if (lane == 0) inv_s[warp] = denom > 0.f ? 1.f / fmaxf(denom, 1e-30f) : 0.f;
@@ -466,23 +481,19 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
     const int h = e >> 7, d = e & 127;
     const float *src = p.part_acc + (row0 + (int64_t)h * p.num_splits) * 128 + d;
     float a = 0.f;
-    for (int c0 = 0; c0 < chunks; c0 += 16) {              // 16 loads in flight
-      float v[16];
+    for (int c0 = 0; c0 < chunks; c0 += 32) {              // 32 loads in flight
+      float v[32];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = c0 + i < chunks ? __ldcg(src + (int64_t)(c0 + i) * 128) : 0.f;
+      for (int i = 0; i < 32; ++i) v[i] = c0 + i < chunks ? __ldcg(src + (int64_t)(c0 + i) * 128) : 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) a = fmaf(c0 + i < chunks ? w_s[h][c0 + i] : 0.f, v[i], a);
+      for (int i = 0; i < 32; ++i) a = fmaf(c0 + i < chunks ? w_s[h][c0 + i] : 0.f, v[i], a);
     }
     a_s[h][d] = a * inv_s[h];
   }
   __syncthreads();
-  const int col = tid & 127, part = tid >> 7;
   float o[8];
 #pragma unroll
   for (int h = 0; h < 8; ++h) o[h] = 0.f;
-  float wv[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) wv[i] = __ldg(p.Pi_v + (part * 32 + i) * 128 + col);
 #pragma unroll
   for (int i = 0; i < 32; ++i)
 #pragma unroll
