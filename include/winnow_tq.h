@@ -128,6 +128,27 @@ int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], void *out,
                int num_splits, void *workspace, size_t workspace_bytes, int32_t *status,
                void *stream);
 
+/* wtq_decode without a caller-supplied workspace.  It has no counterpart in the
+ * reference.  It exists for hosts that cannot allocate device memory for this
+ * library (a server whose arena owns all of it, a loop that may not take the
+ * device-wide synchronisation an allocation implies): the workspace is a
+ * 16 MiB array built into the library image, which every GPU that loads the
+ * library holds until the process exits.  Same arguments and results as
+ * wtq_decode minus the workspace pair.  Calls whose workspace
+ * (wtq_decode_workspace_bytes for the chosen num_splits) exceeds
+ * wtq_decode_static_capacity() are refused with WTQ_ERR_WORKSPACE.  The first
+ * call on each device looks the array's device address up (with that device
+ * current); make that first call before any stream capture begins.  All calls
+ * on a device share the one array: calls that can overlap on the GPU (two
+ * streams, two threads) race and must be serialised by the caller.  Nothing
+ * here calls cudaMalloc, cudaFree or any allocating routine. */
+size_t wtq_decode_static_capacity(void);
+int wtq_decode_static(const void *q, int dtype, const int64_t q_strides[2], void *out,
+                      const int64_t out_strides[2], const wtq_side_t *k_side,
+                      const wtq_side_t *v_side, const int32_t *page_table, int64_t table_stride,
+                      const int32_t *seq_lens, float scale, int B, int Hq, int Hkv, int D, int S,
+                      int P, int max_pages, int num_splits, int32_t *status, void *stream);
+
 /* Replaces tq_dequant / tq_dequant_cuda (turboquant_kv/kernel.py:78-115,
  * turboquant_kv/csrc/tq_dequant.cu:186-211): N packed rows -> (N, D) of
  * `out_dtype`.  Logical row r is read from source row (r / L) * MAXLEN + r % L

@@ -1,0 +1,81 @@
+"""wtq_decode_static, the decode entry point for hosts that may not allocate
+device memory (its workspace is an array inside the library image): called
+through the C ABI twice in a row and compared with wtq_decode, which takes a
+caller-allocated workspace.  Collected last on purpose."""
+import ctypes
+
+import pytest
+import torch
+
+import cases
+from helpers import oracle_case, to_device
+from oracle import tq_oracle as orc
+from winnow_b200 import _lib
+from winnow_b200.packed_attention_cuda import _side, packed_decode_attention
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def call_static(q, kv, scale, num_splits=0):
+    """One call of wtq_decode_static with raw pointers; allocates only `out`."""
+    B, Hq, _, D = q.shape
+    out = torch.empty_like(q)
+    k_side = _side(kv.k_pages, kv.k_norms, kv.k_quant)
+    v_side = _side(kv.v_pages, kv.v_norms, kv.v_quant)
+    rc = _lib.lib().wtq_decode_static(
+        q.data_ptr(), _lib.dtype_code(q.dtype), _lib.i64x(q.stride(0), q.stride(1)),
+        out.data_ptr(), _lib.i64x(out.stride(0), out.stride(1)),
+        ctypes.byref(k_side), ctypes.byref(v_side), kv.page_table.data_ptr(),
+        kv.page_table.stride(0), kv.seq_lens.data_ptr(), float(scale), B, Hq,
+        kv.num_kv_heads, D, kv.page_size, kv.k_pages.shape[0], kv.page_table.shape[1],
+        num_splits, None, _lib.stream_ptr(q.device))
+    return rc, out
+
+
+@pytest.mark.parametrize("name", ["val_long", "qwen7b_gqa_mixed"])     # tensor-core and generic path
+def test_static_workspace_matches_wtq_decode_twice(name):
+    c = next(x for x in cases.ATTENTION_CASES if x.name == name)
+    q, okv, _ = oracle_case(c)
+    kv, scale = to_device(okv, DEV), orc.default_scale(c.D)
+    qd = q.to(DEV)
+    expect = packed_decode_attention(qd, kv, scale)
+    rc, first = call_static(qd, kv, scale)
+    assert rc == 0, _lib.lib().wtq_last_error()
+    # second call: other data and another split count over the same array, which
+    # still holds the first call's partial states
+    q2 = (qd * 0.5 + 0.25).contiguous()
+    expect2 = packed_decode_attention(q2, kv, scale, num_splits=2)
+    rc, second = call_static(q2, kv, scale, num_splits=2)
+    assert rc == 0, _lib.lib().wtq_last_error()
+    torch.cuda.synchronize()
+    for got, ref in ((first, expect), (second, expect2)):
+        assert torch.isfinite(got).all()
+        assert (got.float() - ref.float()).abs().max().item() <= 2e-3
+    for b, L in enumerate(c.lens):
+        if L == 0:
+            assert (first[b] == 0).all() and (second[b] == 0).all()
+
+
+def test_static_workspace_refuses_oversized_calls():
+    lib = _lib.lib()
+    cap = lib.wtq_decode_static_capacity()
+    assert cap == 16 << 20
+    # 64 sequences x 64 heads x 256 splits of fp32 partial rows is far beyond 16 MiB
+    assert lib.wtq_decode_workspace_bytes(64, 64, 8, 128, 8192, 16, 256) > cap
+    q = torch.zeros(64, 64, 1, 128, device=DEV)
+    c = cases.ATTENTION_CASES[5]
+    _, okv, _ = oracle_case(c)
+    kv = to_device(okv, DEV)
+    big_table = torch.full((64, 8192), -1, dtype=torch.int32, device=DEV)
+    kv.page_table, kv.seq_lens = big_table, torch.zeros(64, dtype=torch.int32, device=DEV)
+    B, Hq, _, D = q.shape
+    k_side = _side(kv.k_pages, kv.k_norms, kv.k_quant)
+    v_side = _side(kv.v_pages, kv.v_norms, kv.v_quant)
+    out = torch.empty_like(q)
+    rc = lib.wtq_decode_static(
+        q.data_ptr(), 0, _lib.i64x(q.stride(0), q.stride(1)), out.data_ptr(),
+        _lib.i64x(out.stride(0), out.stride(1)), ctypes.byref(k_side), ctypes.byref(v_side),
+        kv.page_table.data_ptr(), kv.page_table.stride(0), kv.seq_lens.data_ptr(), 1.0, B, Hq,
+        8, D, 16, kv.k_pages.shape[0], 8192, 256, None, _lib.stream_ptr(q.device))
+    assert rc == -4 and b"16777216" in lib.wtq_last_error()

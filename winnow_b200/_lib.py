@@ -51,6 +51,12 @@ _SIGNATURES = {
     "wtq_profile_enable": (c_int, [c_int]),
     "wtq_profile_collect": (c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
     "wtq_profile_disable": (c_int, []),
+    "wtq_decode_static_capacity": (c_size_t, []),
+    "wtq_decode_static": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p,
+                                  ctypes.POINTER(c_int64), ctypes.POINTER(Side),
+                                  ctypes.POINTER(Side), c_void_p, c_int64, c_void_p, c_float,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                  c_void_p]),
     "wtq_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int64, c_int64, c_int64, c_void_p]),
 }
