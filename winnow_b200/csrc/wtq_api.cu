@@ -63,11 +63,12 @@ extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pag
   if (B < 1 || Hkv < 1 || Hq < 1) return 1;
   const int64_t groups = (int64_t)B * Hkv;
   const int64_t max_tokens = (int64_t)max_pages * S;
-  if (D == 128 && bw_k == 4 && bw_v == 4 && S >= 16 && (S & (S - 1)) == 0 && Hq / Hkv <= 8) {
-    // tensor-core path: every warp of the persistent grid (16 per SM) should see
+  const int warps = mma_warps_per_sm(bw_k, bw_v);
+  if (D == 128 && warps > 0 && S >= 16 && (S & (S - 1)) == 0 && Hq / Hkv <= 8) {
+    // tensor-core path: every warp of the persistent grid should see
     // about three chunks, and a chunk should be long enough (>= 256 tokens)
     // that writing its partial state stays small beside reading its pages
-    const int64_t workers = (int64_t)device_sms() * 16;
+    const int64_t workers = (int64_t)device_sms() * warps;
     int64_t chunk = (max_tokens * groups + 3 * workers - 1) / (3 * workers);
     chunk = (chunk + 63) / 64 * 64;
     if (chunk < 256) chunk = 256;
@@ -152,12 +153,12 @@ extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], 
   m.part_acc = p.part_acc; m.part_m = p.part_m; m.part_l = p.part_l;
   m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
   m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
-  const bool fast = mma4_eligible(p) && !force_generic();
+  const bool fast = mma_eligible(p) && !force_generic();
   // the tensor-core path works in the exp2 domain: fold log2(e) into the query
   const float q_scale = fast ? scale * 1.4426950408889634f : scale;
   if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, q_scale, B, Hq, D, q_rot, stream))
     return rc;
-  if (fast) return launch_decode_mma4(p, m, stream);
+  if (fast) return launch_decode_mma(p, m, stream);
   if (int rc = launch_decode_generic(p, stream)) return rc;
   return launch_merge(m, B, stream);
 }

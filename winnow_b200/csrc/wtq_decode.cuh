@@ -43,11 +43,12 @@ int launch_rotate_q(const void *q, int dtype, const int64_t *q_strides, const fl
 int launch_decode_generic(const DecodeParams &p, cudaStream_t stream);
 int launch_merge(const MergeParams &p, int B, cudaStream_t stream);
 
-// 4-bit / head_dim 128 tensor-core path (wtq_decode_mma.cu).  In that path
-// `num_splits` counts chunks of mma4_chunk_tokens() tokens per sequence, the
-// partial m values are in the log2 domain and q_rot carries scale * log2(e).
-bool mma4_eligible(const DecodeParams &p);
-int mma4_chunk_tokens(int max_tokens, int splits);
-int launch_decode_mma4(const DecodeParams &p, const MergeParams &m, cudaStream_t stream);
+// head_dim 128 tensor-core path (wtq_decode_mma.cu).  In that path `num_splits`
+// counts chunks of mma_chunk_tokens() tokens per sequence, the partial m values
+// are in the log2 domain and q_rot carries scale * log2(e).
+int mma_warps_per_sm(int bw_k, int bw_v);
+bool mma_eligible(const DecodeParams &p);
+int mma_chunk_tokens(int max_tokens, int splits);
+int launch_decode_mma(const DecodeParams &p, const MergeParams &m, cudaStream_t stream);
 
 }  // namespace wtq

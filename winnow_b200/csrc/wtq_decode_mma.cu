@@ -1,9 +1,9 @@
-// Split-K decode attention over paged packed K/V: the sm_100a fast path for
-// head_dim 128, 4-bit keys and values, pages of 16, 32, 64, ... tokens and a
-// GQA group of at most 8 query heads.
+// Split-K decode attention over paged packed K/V: the sm_100a tensor-core path
+// for head_dim 128, key/value widths of 4, 6 or 8 bits (4/4, 4/6, 6/6, 8/8),
+// pages of 16, 32, 64, ... tokens and a GQA group of at most 8 query heads.
 //
-// One persistent CTA per SM, 16 warps.  A warp is an independent worker: it
-// takes (sequence, kv head, chunk of tokens) items round-robin, streams the
+// One persistent CTA per SM, up to 16 warps.  A warp is an independent worker:
+// it takes (sequence, kv head, chunk of tokens) items round-robin, streams the
 // chunk's 16-token tiles from HBM into its private shared-memory ring with
 // 16-byte cp.async copies (the next 32 tokens are in flight while the current
 // 32 are consumed), and keeps the whole flash-decoding state in registers.
@@ -12,44 +12,70 @@
 //   scores   S^T[16 tok x 8 heads] = C_K[16 x 128] . Qrot^T   8 x mma.m16n8k16
 //   softmax  online, fp32, exp2 domain, max shared by shuffles
 //   values   O^T[128 d x 8 heads] += C_V^T[128 x 16 tok] . P'^T   8 x mma
-// The fp16 operands C_K / C_V are produced from the 4-bit codes by ONE
-// shared-memory lookup per packed byte (= two codes): a 256-entry table of
-// half2 {centroid[lo nibble], centroid[hi nibble]}, replicated per lane so
-// that every lookup of a warp is bank-conflict free, and placed at shared
-// address 0x10000 so that one byte-permute builds the address
-// (0x10000 | byte << 8 | table << 7 | lane << 2).
-//   * keys: a byte holds two adjacent coordinates of one token, which is the
-//     pair an A-fragment register of the score MMA wants (the contraction runs
-//     over coordinates, whose order is free: q is permuted to match);
-//   * values: the contraction runs over tokens, so a register must hold one
-//     coordinate of two tokens; the low (high) nibbles of the same byte of two
-//     tokens are merged by one shift and one bit-select into a byte that
-//     indexes the same table.
+// The fp16 operands C_K / C_V come from shared-memory tables replicated per
+// lane (every lookup of a warp is bank-conflict free) that start at shared
+// address 0x10000, so that the address of an entry is
+// 0x10000 | index << 8 | side << 7 | lane << 2 and needs no addition.
+//   4-bit: ONE lookup per packed byte (= two codes) into a 256-entry table of
+//     half2 {centroid[lo nibble], centroid[hi nibble]}; one byte-permute builds
+//     the address.  Keys: a byte holds two adjacent coordinates of one token,
+//     which is the pair an A-fragment register of the score MMA wants (the
+//     contraction runs over coordinates, whose order is free: q is permuted to
+//     match).  Values: the contraction runs over tokens, so a register must
+//     hold one coordinate of two tokens; the low (high) nibbles of the same
+//     byte of two tokens are merged by one shift and one bit-select into a byte
+//     that indexes the same table.
+//   6- and 8-bit: one lookup per code into a table of half2 {c, c}; a shift
+//     and a mask (8-bit: a byte-permute) build the address and one
+//     byte-permute joins two results into an operand register.
 // mma.sync is the right tensor instruction here: the operands are born in
 // registers; tcgen05 would need them written back to shared memory first.
 //
 // Reference schedule being reproduced: turboquant_kv/packed_attention.py:
 // 260-334 (tiled online softmax), split merge :328-334.
+#include <type_traits>
+
 #include "wtq_decode.cuh"
 
 namespace wtq {
 
-namespace mma4 {
+namespace mma {
 
-constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
 constexpr int kTileTokens = 16;
 constexpr int kTilesPerIter = 2;                       // 32 tokens per iteration
 constexpr int kIterTokens = kTileTokens * kTilesPerIter;
-constexpr int kVRow = 80;                              // padded value row (bank spread)
-constexpr int kOffV = 1024;                            // tile slot: K | V | nK | nV
-constexpr int kOffNK = kOffV + kTileTokens * kVRow;    // 2304
-constexpr int kOffNV = kOffNK + 32;                    // 2336
-constexpr int kSlot = kOffNV + 32;                     // 2368 bytes
-constexpr int kRing = 2 * kTilesPerIter * kSlot;       // two iterations per warp
-constexpr uint32_t kLutAddr = 0x10000;                 // shared address of the table
-constexpr uint32_t kLutBytes = 0x10000;
-constexpr float kPreciseAbove = 8.0f;                  // |score| (log2 units) that triggers fp32 rescoring
+constexpr uint32_t kLutAddr = 0x10000;                 // shared address of the tables
+constexpr uint32_t kRingLow = 2048;                    // rings start here (>= dynamic smem base)
+constexpr uint32_t kSmemLimit = 227 * 1024;
+constexpr float kPreciseAbove = 8.0f;   // |score| (log2 units) that triggers fp32 rescoring
+
+constexpr int lut_entries(int bw) { return bw == 4 ? 256 : (1 << bw); }
+constexpr int cmax(int a, int b) { return a > b ? a : b; }
+constexpr int cmin(int a, int b) { return a < b ? a : b; }
+
+// Shared-memory plan of one (key width, value width) instantiation.
+template <int BWK, int BWV> struct Cfg {
+  static constexpr int NBK = 16 * BWK, NBV = 16 * BWV;          // bytes per packed row
+  static constexpr int kVRow = BWV == 4 ? 80 : NBV;             // 4-bit value rows are padded
+  static constexpr int kOffV = kTileTokens * NBK;               // tile slot: K | V | nK | nV
+  static constexpr int kOffNK = kOffV + kTileTokens * kVRow;
+  static constexpr int kOffNV = kOffNK + 32;
+  static constexpr int kSlot = kOffNV + 32;
+  static constexpr int kRing = 2 * kTilesPerIter * kSlot;       // two iterations per warp
+  static constexpr uint32_t kLutBytes = cmax(lut_entries(BWK), lut_entries(BWV)) * 256u;
+  static constexpr int kRingsBelow = (int)((kLutAddr - kRingLow) / kRing);
+  static constexpr int kRingsAbove = (int)((kSmemLimit - kLutAddr - kLutBytes) / kRing);
+  static constexpr int kWarps = cmin(16, kRingsBelow + kRingsAbove);
+  static constexpr int kThreads = kWarps * 32;
+  static constexpr size_t kDynamicSmem =
+      kLutAddr + kLutBytes + (size_t)cmax(kWarps - kRingsBelow, 0) * kRing;
+  static_assert(kWarps >= 8, "too few warps fit");
+  static_assert(kDynamicSmem <= kSmemLimit, "shared memory budget");
+  __device__ static uint32_t ring_address(int w) {
+    return w < kRingsBelow ? kRingLow + (uint32_t)w * kRing
+                           : kLutAddr + kLutBytes + (uint32_t)(w - kRingsBelow) * kRing;
+  }
+};
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
@@ -74,6 +100,11 @@ __device__ __forceinline__ uint2 lds64(uint32_t a) {
 __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(a));
   return v;
 }
 __device__ __forceinline__ float lds_half(uint32_t a) {
@@ -106,28 +137,155 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&h);
 }
-// Table lookup of byte `K` (0..3) of `word`: `lane_sel` carries 0x10000, the
-// table bit and the lane's bank.
-template <int K> __device__ __forceinline__ uint32_t lut(uint32_t word, uint32_t lane_sel) {
-  return lds32(__byte_perm(word, lane_sel, 0x7604 | (K << 4)));
+
+// ---- table lookups ----------------------------------------------------------
+// `sel` carries 0x10000, the side bit (values: 0x80) and the lane's bank.
+// 4-bit: entry of byte K (0..3) of `word`, a half2 of the byte's two codes.
+template <int K> __device__ __forceinline__ uint32_t lut_byte(uint32_t word, uint32_t sel) {
+  return lds32(__byte_perm(word, sel, 0x7604 | (K << 4)));
+}
+// 6/8-bit: entry {c, c} of code I of the bit stream held in w[0..NW).
+template <int BW, int I, int NW>
+__device__ __forceinline__ uint32_t lut_code(const uint32_t (&w)[NW], uint32_t sel) {
+  constexpr int bit = I * BW, word = bit / 32, off = bit % 32;
+  static_assert(word < NW, "code outside the words held");
+  if constexpr (BW == 8) {
+    return lds32(__byte_perm(w[word], sel, 0x7604 | ((off / 8) << 4)));
+  } else {
+    constexpr uint32_t mask = ((1u << BW) - 1u) << 8;
+    uint32_t x;
+    if constexpr (off + BW <= 32) {
+      x = off >= 8 ? (w[word] >> (off >= 8 ? off - 8 : 0)) : (w[word] << (off < 8 ? 8 - off : 0));
+    } else {                                     // the code straddles two words
+      x = __funnelshift_r(w[word], w[word + 1 < NW ? word + 1 : word], off - 8);
+    }
+    return lds32((x & mask) | sel);
+  }
+}
+// low half of x joined with the high half of y
+__device__ __forceinline__ uint32_t join(uint32_t x, uint32_t y) {
+  return __byte_perm(x, y, 0x7610);
 }
 
-}  // namespace mma4
+// Words of a lane's share of a packed row: NBYTES at shared address a.
+template <int NBYTES>
+__device__ __forceinline__ void load_words(uint32_t a, uint32_t (&w)[NBYTES / 4]) {
+  if constexpr (NBYTES % 16 == 0) {
+#pragma unroll
+    for (int i = 0; i < NBYTES / 16; ++i) {
+      const uint4 v = lds128(a + 16 * i);
+      w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+    }
+  } else if constexpr (NBYTES % 8 == 0) {
+#pragma unroll
+    for (int i = 0; i < NBYTES / 8; ++i) {
+      const uint2 v = lds64(a + 8 * i);
+      w[2 * i] = v.x; w[2 * i + 1] = v.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NBYTES / 4; ++i) w[i] = lds32(a + 4 * i);
+  }
+}
 
-using namespace mma4;
+}  // namespace mma
 
-// Rings live at fixed shared addresses: as many as fit between kRingLow and the
-// table, the rest after the table.  Dynamic shared memory starts at a small
-// driver-defined address (checked in the kernel to be <= kRingLow).
-constexpr uint32_t kRingLow = 2048;
-constexpr int kRingsBelow = (int)((kLutAddr - kRingLow) / kRing);
-constexpr int kRingsAbove = kWarps > kRingsBelow ? kWarps - kRingsBelow : 0;
-constexpr size_t kDynamicSmem = kLutAddr + kLutBytes + (size_t)kRingsAbove * kRing;
-static_assert(kDynamicSmem <= 227 * 1024, "shared memory budget");
+using namespace mma;
 
-__device__ __forceinline__ uint32_t ring_address(int w) {
-  return w < kRingsBelow ? kRingLow + (uint32_t)w * kRing
-                         : kLutAddr + kLutBytes + (uint32_t)(w - kRingsBelow) * kRing;
+// A-fragment registers of the score MMA for contraction step KS (0..7): the
+// lane holds 32 codes (coordinates 32t..32t+31) of token rows g (w0) and g+8
+// (w1); step KS consumes codes 4KS..4KS+3 of each.
+template <int BW, int KS, int NW>
+__device__ __forceinline__ void key_fragment(const uint32_t (&w0)[NW], const uint32_t (&w1)[NW],
+                                             uint32_t sel, uint32_t (&a)[4]) {
+  if constexpr (BW == 4) {
+    constexpr int j = KS / 2, e = 2 * (KS % 2);
+    a[0] = lut_byte<e>(w0[j], sel);
+    a[1] = lut_byte<e>(w1[j], sel);
+    a[2] = lut_byte<e + 1>(w0[j], sel);
+    a[3] = lut_byte<e + 1>(w1[j], sel);
+  } else {
+    constexpr int i = 4 * KS;
+    a[0] = join(lut_code<BW, i>(w0, sel), lut_code<BW, i + 1>(w0, sel));
+    a[1] = join(lut_code<BW, i>(w1, sel), lut_code<BW, i + 1>(w1, sel));
+    a[2] = join(lut_code<BW, i + 2>(w0, sel), lut_code<BW, i + 3>(w0, sel));
+    a[3] = join(lut_code<BW, i + 2>(w1, sel), lut_code<BW, i + 3>(w1, sel));
+  }
+}
+
+// Value side of one tile: the lane holds coordinates 16g..16g+15 of tokens
+// 2t, 2t+1 (A, B) and 2t+8, 2t+9 (C, D).  MMA j (0..7) takes coordinates
+// 16g+2j (row g) and 16g+2j+1 (row g+8) of the output tile.
+template <int BW, int VROW>
+__device__ __forceinline__ void value_mmas(uint32_t vbase, int g, int t, uint32_t sel,
+                                           uint32_t pb0, uint32_t pb1, float (&acc)[8][4]) {
+  constexpr int NB8 = 2 * BW;                       // bytes of 16 codes
+  const uint32_t at = vbase + g * NB8;
+  if constexpr (BW == 4) {
+    const uint2 wa = lds64(at + (2 * t) * VROW), wb = lds64(at + (2 * t + 1) * VROW);
+    const uint2 wc = lds64(at + (2 * t + 8) * VROW), wd = lds64(at + (2 * t + 9) * VROW);
+    // byte j of lo_* : low nibbles of tokens (A | B << 4) at coordinate 16g+2j
+    // byte j of hi_* : high nibbles, coordinate 16g+2j+1
+    const uint32_t lo_ab[2] = {(wa.x & 0x0F0F0F0Fu) | ((wb.x << 4) & 0xF0F0F0F0u),
+                               (wa.y & 0x0F0F0F0Fu) | ((wb.y << 4) & 0xF0F0F0F0u)};
+    const uint32_t hi_ab[2] = {((wa.x >> 4) & 0x0F0F0F0Fu) | (wb.x & 0xF0F0F0F0u),
+                               ((wa.y >> 4) & 0x0F0F0F0Fu) | (wb.y & 0xF0F0F0F0u)};
+    const uint32_t lo_cd[2] = {(wc.x & 0x0F0F0F0Fu) | ((wd.x << 4) & 0xF0F0F0F0u),
+                               (wc.y & 0x0F0F0F0Fu) | ((wd.y << 4) & 0xF0F0F0F0u)};
+    const uint32_t hi_cd[2] = {((wc.x >> 4) & 0x0F0F0F0Fu) | (wd.x & 0xF0F0F0F0u),
+                               ((wc.y >> 4) & 0x0F0F0F0Fu) | (wd.y & 0xF0F0F0F0u)};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mma16816(acc[4 * h + 0], lut_byte<0>(lo_ab[h], sel), lut_byte<0>(hi_ab[h], sel),
+               lut_byte<0>(lo_cd[h], sel), lut_byte<0>(hi_cd[h], sel), pb0, pb1);
+      mma16816(acc[4 * h + 1], lut_byte<1>(lo_ab[h], sel), lut_byte<1>(hi_ab[h], sel),
+               lut_byte<1>(lo_cd[h], sel), lut_byte<1>(hi_cd[h], sel), pb0, pb1);
+      mma16816(acc[4 * h + 2], lut_byte<2>(lo_ab[h], sel), lut_byte<2>(hi_ab[h], sel),
+               lut_byte<2>(lo_cd[h], sel), lut_byte<2>(hi_cd[h], sel), pb0, pb1);
+      mma16816(acc[4 * h + 3], lut_byte<3>(lo_ab[h], sel), lut_byte<3>(hi_ab[h], sel),
+               lut_byte<3>(lo_cd[h], sel), lut_byte<3>(hi_cd[h], sel), pb0, pb1);
+    }
+  } else {
+    constexpr int NW = NB8 / 4;
+    uint32_t wa[NW], wb[NW], wc[NW], wd[NW];
+    load_words<NB8>(at + (2 * t) * VROW, wa);
+    load_words<NB8>(at + (2 * t + 1) * VROW, wb);
+    load_words<NB8>(at + (2 * t + 8) * VROW, wc);
+    load_words<NB8>(at + (2 * t + 9) * VROW, wd);
+    auto one = [&](auto jc) {
+      constexpr int j = decltype(jc)::value;
+      mma16816(acc[j],
+               join(lut_code<BW, 2 * j>(wa, sel), lut_code<BW, 2 * j>(wb, sel)),
+               join(lut_code<BW, 2 * j + 1>(wa, sel), lut_code<BW, 2 * j + 1>(wb, sel)),
+               join(lut_code<BW, 2 * j>(wc, sel), lut_code<BW, 2 * j>(wd, sel)),
+               join(lut_code<BW, 2 * j + 1>(wc, sel), lut_code<BW, 2 * j + 1>(wd, sel)), pb0, pb1);
+    };
+    one(std::integral_constant<int, 0>{}); one(std::integral_constant<int, 1>{});
+    one(std::integral_constant<int, 2>{}); one(std::integral_constant<int, 3>{});
+    one(std::integral_constant<int, 4>{}); one(std::integral_constant<int, 5>{});
+    one(std::integral_constant<int, 6>{}); one(std::integral_constant<int, 7>{});
+  }
+}
+
+// Scores of one tile: S^T fragment (rows g, g+8; heads 2t, 2t+1), unscaled.
+template <int BW>
+__device__ __forceinline__ void key_mmas(uint32_t kbase, int g, int t, uint32_t sel,
+                                         const uint32_t (&qf)[8][2], float (&c)[4]) {
+  constexpr int NB4 = 4 * BW;                       // bytes of 32 codes
+  constexpr int NW = NB4 / 4, NB = 16 * BW;
+  uint32_t w0[NW], w1[NW];
+  load_words<NB4>(kbase + g * NB + t * NB4, w0);
+  load_words<NB4>(kbase + (g + 8) * NB + t * NB4, w1);
+  auto one = [&](auto ksc) {
+    constexpr int ks = decltype(ksc)::value;
+    uint32_t a[4];
+    key_fragment<BW, ks>(w0, w1, sel, a);
+    mma16816(c, a[0], a[1], a[2], a[3], qf[ks][0], qf[ks][1]);
+  };
+  one(std::integral_constant<int, 0>{}); one(std::integral_constant<int, 1>{});
+  one(std::integral_constant<int, 2>{}); one(std::integral_constant<int, 3>{});
+  one(std::integral_constant<int, 4>{}); one(std::integral_constant<int, 5>{});
+  one(std::integral_constant<int, 6>{}); one(std::integral_constant<int, 7>{});
 }
 
 // fp32 scores of tile rows g and g+8 against two query rows (already rotated
@@ -135,26 +293,35 @@ __device__ __forceinline__ uint32_t ring_address(int w) {
 // row g+8 . qa, row g+8 . qb}.  Kept out of line: it runs only for windows
 // whose fp16 scores came out large, and must not cost the common path
 // registers.
-__device__ __noinline__ float4 precise_scores(uint32_t slot, int g, const float *qa,
-                                              const float *qb, const float *centroids) {
+template <int BW>
+__device__ __noinline__ float4 precise_scores(uint32_t kbase, uint32_t nk_addr, int g,
+                                              const float *qa, const float *qb,
+                                              const float *centroids) {
+  constexpr int NB = 16 * BW;
   float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+  const uint32_t r0 = kbase + g * NB, r1 = kbase + (g + 8) * NB;
 #pragma unroll 1
-  for (int w = 0; w < 16; ++w) {                       // 16 words of 8 codes per row
-    uint32_t x0 = lds32(slot + g * 64 + w * 4), x1 = lds32(slot + (g + 8) * 64 + w * 4);
-#pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const float c0 = __ldg(centroids + (x0 & 15u)), c1 = __ldg(centroids + (x1 & 15u));
-      const float fa = __ldg(qa + w * 8 + n), fb = __ldg(qb + w * 8 + n);
-      d0 = fmaf(fa, c0, d0); d1 = fmaf(fb, c0, d1);
-      d2 = fmaf(fa, c1, d2); d3 = fmaf(fb, c1, d3);
-      x0 >>= 4; x1 >>= 4;
+  for (int d = 0; d < 128; ++d) {
+    const int bit = d * BW, b0 = bit >> 3, sh = bit & 7;
+    uint32_t x0 = lds_u8(r0 + b0), x1 = lds_u8(r1 + b0);
+    if (sh + BW > 8) {
+      x0 |= lds_u8(r0 + b0 + 1) << 8;
+      x1 |= lds_u8(r1 + b0 + 1) << 8;
     }
+    const float c0 = __ldg(centroids + ((x0 >> sh) & ((1u << BW) - 1u)));
+    const float c1 = __ldg(centroids + ((x1 >> sh) & ((1u << BW) - 1u)));
+    const float fa = __ldg(qa + d), fb = __ldg(qb + d);
+    d0 = fmaf(fa, c0, d0); d1 = fmaf(fb, c0, d1);
+    d2 = fmaf(fa, c1, d2); d3 = fmaf(fb, c1, d3);
   }
-  const float nk0 = lds_half(slot + kOffNK + g * 2), nk1 = lds_half(slot + kOffNK + (g + 8) * 2);
+  const float nk0 = lds_half(nk_addr + g * 2), nk1 = lds_half(nk_addr + (g + 8) * 2);
   return make_float4(d0 * nk0, d1 * nk0, d2 * nk1, d3 * nk1);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p, int chunk_tokens) {
+template <int BWK, int BWV>
+__global__ void __launch_bounds__(Cfg<BWK, BWV>::kThreads, 1)
+decode_mma_kernel(DecodeParams p, int chunk_tokens) {
+  using C = Cfg<BWK, BWV>;
   extern __shared__ __align__(16) uint8_t dyn_smem[];
   const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(dyn_smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -164,23 +331,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
     return;
   }
 
-  // ---- byte -> half2 tables, one copy per lane: [byte][K|V][lane] -----------
-  for (int e = tid; e < 256 * 64; e += kThreads) {
-    const int byte = e >> 6, side = (e >> 5) & 1;
+  // ---- tables, one copy per lane: [index][K|V][lane] -------------------------
+  for (int e = tid; e < (int)(C::kLutBytes / 4); e += C::kThreads) {
+    const int index = e >> 6, side = (e >> 5) & 1;
+    const int bw = side ? BWV : BWK;
     const float *cent = side ? p.v.centroids : p.k.centroids;
-    sts32(kLutAddr + (uint32_t)e * 4u, pack_half2(cent[byte & 15], cent[byte >> 4]));
+    uint32_t v = 0;
+    if (bw == 4) v = pack_half2(cent[index & 15], cent[index >> 4]);
+    else if (index < (1 << bw)) v = pack_half2(cent[index], cent[index]);
+    sts32(kLutAddr + (uint32_t)e * 4u, v);
   }
   __syncthreads();
 
-  const uint32_t ring = ring_address(warp);
+  const uint32_t ring = C::ring_address(warp);
   const uint32_t sel_k = 0x10000u | (uint32_t)(lane << 2);
   const uint32_t sel_v = sel_k | 0x80u;
   const int S = p.S;
   const int s_shift = 31 - __clz(S);                 // S is a power of two (checked by the host)
-  const uint32_t v_dst = (uint32_t)(g * kVRow + t * 16);
   const int chunks = p.num_splits;
   const int64_t items = (int64_t)p.B * p.Hkv * chunks;
-  const int workers = gridDim.x * kWarps;
+  const int workers = gridDim.x * C::kWarps;
 
   // q_rot is written by the kernel launched just before this one; everything
   // above overlapped with its tail.  The merge that follows may be scheduled as
@@ -228,11 +398,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
     const __half *nv_head = p.v.norms + (int64_t)kvh * p.v.norm_head_stride;
     const int32_t *table = p.page_table + (int64_t)b * p.table_stride;
 
-    // Copies of one iteration (4 tiles) into half `buf` of the ring.  Lane l
-    // moves key chunks l and l+32 (exactly the 32 bytes it reads back itself),
-    // the same chunks of the values into padded rows, and lanes 0..3 the norms.
-    // Returns a bit per tile: set when the tile's page id was inside the pool
-    // and its copies were issued.
+    // Copies of one iteration into half `buf` of the ring: a tile's key rows
+    // and value rows are contiguous in HBM (16 rows of NB bytes); lane l moves
+    // 16-byte chunks l, l+32, ...; lanes 0..3 also move the norms.  Returns a
+    // bit per tile: set when the tile's page id was inside the pool.
     auto issue = [&](int it, int buf) -> uint32_t {
       uint32_t loaded = 0;
       if (it < n_iter) {
@@ -244,18 +413,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
             const int pid = table[tok >> s_shift];
             if (pid >= 0 && pid < p.P) {
               loaded |= 1u << u;
-              const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
-              const uint8_t *ks = k_head + (int64_t)pid * p.k.page_stride + (sub * 64 + lane * 16);
-              const uint8_t *vs = v_head + (int64_t)pid * p.v.page_stride + (sub * 64 + lane * 16);
-              cp_async16(dst + lane * 16, ks);
-              cp_async16(dst + 512 + lane * 16, ks + 512);
-              cp_async16(dst + kOffV + v_dst, vs);
-              cp_async16(dst + kOffV + 8 * kVRow + v_dst, vs + 512);
+              const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
+              const uint8_t *ks = k_head + (int64_t)pid * p.k.page_stride + (sub * C::NBK + lane * 16);
+              const uint8_t *vs = v_head + (int64_t)pid * p.v.page_stride + (sub * C::NBV + lane * 16);
+#pragma unroll
+              for (int i = 0; i < C::NBK / 32; ++i)
+                cp_async16(dst + lane * 16 + i * 512, ks + i * 512);
+#pragma unroll
+              for (int i = 0; i < C::NBV / 32; ++i) {
+                if constexpr (BWV == 4)      // chunk c -> padded row c/4, quarter c%4
+                  cp_async16(dst + C::kOffV + (g + 8 * i) * C::kVRow + t * 16, vs + i * 512);
+                else
+                  cp_async16(dst + C::kOffV + lane * 16 + i * 512, vs + i * 512);
+              }
               if (lane < 2)
-                cp_async16(dst + kOffNK + lane * 16,
+                cp_async16(dst + C::kOffNK + lane * 16,
                            nk_head + (int64_t)pid * p.k.norm_page_stride + sub + lane * 8);
               else if (lane < 4)
-                cp_async16(dst + kOffNV + (lane - 2) * 16,
+                cp_async16(dst + C::kOffNV + (lane - 2) * 16,
                            nv_head + (int64_t)pid * p.v.norm_page_stride + sub + (lane - 2) * 8);
             } else if (p.status && lane == 0) {
               atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
@@ -275,31 +450,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
       cp_async_wait<1>();
       __syncwarp();
 
-      // ---- scores of the 4 tiles ------------------------------------------
+      // ---- scores of the tiles ----------------------------------------------
       float s[kTilesPerIter][4];
       bool ok[kTilesPerIter][2];
       float big = 0.f;
 #pragma unroll
       for (int u = 0; u < kTilesPerIter; ++u) {
-        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
+        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
         const int tok = tok0 + it * kIterTokens + u * kTileTokens;
         const bool page_ok = (loaded >> u) & 1u;
         ok[u][0] = page_ok && tok + g < tok1;
         ok[u][1] = page_ok && tok + g + 8 < tok1;
-        const uint4 r0 = lds128(slot + g * 64 + t * 16);
-        const uint4 r1 = lds128(slot + (g + 8) * 64 + t * 16);
         float c[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t w0[4] = {r0.x, r0.y, r0.z, r0.w};
-        const uint32_t w1[4] = {r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          mma16816(c, lut<0>(w0[j], sel_k), lut<0>(w1[j], sel_k), lut<1>(w0[j], sel_k),
-                   lut<1>(w1[j], sel_k), qf[2 * j][0], qf[2 * j][1]);
-          mma16816(c, lut<2>(w0[j], sel_k), lut<2>(w1[j], sel_k), lut<3>(w0[j], sel_k),
-                   lut<3>(w1[j], sel_k), qf[2 * j + 1][0], qf[2 * j + 1][1]);
-        }
-        const float nk0 = lds_half(slot + kOffNK + g * 2);
-        const float nk1 = lds_half(slot + kOffNK + (g + 8) * 2);
+        key_mmas<BWK>(slot, g, t, sel_k, qf, c);
+        const float nk0 = lds_half(slot + C::kOffNK + g * 2);
+        const float nk1 = lds_half(slot + C::kOffNK + (g + 8) * 2);
         c[0] *= nk0; c[1] *= nk0; c[2] *= nk1; c[3] *= nk1;
         big = fmaxf(big, ok[u][0] ? fmaxf(fabsf(c[0]), fabsf(c[1])) : 0.f);
         big = fmaxf(big, ok[u][1] ? fmaxf(fabsf(c[2]), fabsf(c[3])) : 0.f);
@@ -313,20 +478,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
       // any score of this window is large (|s| > 8 in log2 units) its tiles are
       // scored again in fp32 on the CUDA cores, so that large logits cost time,
       // not accuracy.
-      {
-        if (__any_sync(0xffffffffu, big > kPreciseAbove)) {
-          const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
-          const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
-          const float *qa = q0 + (h0 ? 2 * t : 0) * 128, *qb = q0 + (h1 ? 2 * t + 1 : 0) * 128;
+      if (__any_sync(0xffffffffu, big > kPreciseAbove)) {
+        const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
+        const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
+        const float *qa = q0 + (h0 ? 2 * t : 0) * 128, *qb = q0 + (h1 ? 2 * t + 1 : 0) * 128;
 #pragma unroll
-          for (int u = 0; u < kTilesPerIter; ++u) {
-            const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
-            const float4 d = precise_scores(slot, g, qa, qb, p.k.centroids);
-            s[u][0] = ok[u][0] ? (h0 ? d.x : 0.f) : -INFINITY;
-            s[u][1] = ok[u][0] ? (h1 ? d.y : 0.f) : -INFINITY;
-            s[u][2] = ok[u][1] ? (h0 ? d.z : 0.f) : -INFINITY;
-            s[u][3] = ok[u][1] ? (h1 ? d.w : 0.f) : -INFINITY;
-          }
+        for (int u = 0; u < kTilesPerIter; ++u) {
+          const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
+          const float4 d = precise_scores<BWK>(slot, slot + C::kOffNK, g, qa, qb, p.k.centroids);
+          s[u][0] = ok[u][0] ? (h0 ? d.x : 0.f) : -INFINITY;
+          s[u][1] = ok[u][0] ? (h1 ? d.y : 0.f) : -INFINITY;
+          s[u][2] = ok[u][1] ? (h0 ? d.z : 0.f) : -INFINITY;
+          s[u][3] = ok[u][1] ? (h1 ? d.w : 0.f) : -INFINITY;
         }
       }
 
@@ -357,45 +520,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma4_kernel(DecodeParams p
       m_run[0] = mx[0];
       m_run[1] = mx[1];
 
-      // ---- values of the 4 tiles ------------------------------------------
+      // ---- values of the tiles ----------------------------------------------
 #pragma unroll
       for (int u = 0; u < kTilesPerIter; ++u) {
-        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * kSlot;
-        const float nv0 = lds_half(slot + kOffNV + g * 2);
-        const float nv1 = lds_half(slot + kOffNV + (g + 8) * 2);
+        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
+        const float nv0 = lds_half(slot + C::kOffNV + g * 2);
+        const float nv1 = lds_half(slot + C::kOffNV + (g + 8) * 2);
         const float p0 = ex2(s[u][0] - base0), p1 = ex2(s[u][1] - base1);
         const float p2 = ex2(s[u][2] - base0), p3 = ex2(s[u][3] - base1);
         l_run[0] += p0 + p2;
         l_run[1] += p1 + p3;
         // rows g / g+8 of P' (token x head) -> B fragment (token pairs of head g)
-        const uint32_t pb0 = movmatrix_trans(
-            ok[u][0] ? pack_half2(p0 * nv0, p1 * nv0) : 0u);
-        const uint32_t pb1 = movmatrix_trans(
-            ok[u][1] ? pack_half2(p2 * nv1, p3 * nv1) : 0u);
-        const uint32_t vb = slot + kOffV + g * 8;
-        const uint2 wa = lds64(vb + (2 * t) * kVRow), wb = lds64(vb + (2 * t + 1) * kVRow);
-        const uint2 wc = lds64(vb + (2 * t + 8) * kVRow), wd = lds64(vb + (2 * t + 9) * kVRow);
-        // byte j of lo_* : low nibbles of tokens (A | B << 4) at coordinate 16g+2j
-        // byte j of hi_* : high nibbles, coordinate 16g+2j+1
-        const uint32_t lo_ab[2] = {(wa.x & 0x0F0F0F0Fu) | ((wb.x << 4) & 0xF0F0F0F0u),
-                                   (wa.y & 0x0F0F0F0Fu) | ((wb.y << 4) & 0xF0F0F0F0u)};
-        const uint32_t hi_ab[2] = {((wa.x >> 4) & 0x0F0F0F0Fu) | (wb.x & 0xF0F0F0F0u),
-                                   ((wa.y >> 4) & 0x0F0F0F0Fu) | (wb.y & 0xF0F0F0F0u)};
-        const uint32_t lo_cd[2] = {(wc.x & 0x0F0F0F0Fu) | ((wd.x << 4) & 0xF0F0F0F0u),
-                                   (wc.y & 0x0F0F0F0Fu) | ((wd.y << 4) & 0xF0F0F0F0u)};
-        const uint32_t hi_cd[2] = {((wc.x >> 4) & 0x0F0F0F0Fu) | (wd.x & 0xF0F0F0F0u),
-                                   ((wc.y >> 4) & 0x0F0F0F0Fu) | (wd.y & 0xF0F0F0F0u)};
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          mma16816(acc[4 * h + 0], lut<0>(lo_ab[h], sel_v), lut<0>(hi_ab[h], sel_v),
-                   lut<0>(lo_cd[h], sel_v), lut<0>(hi_cd[h], sel_v), pb0, pb1);
-          mma16816(acc[4 * h + 1], lut<1>(lo_ab[h], sel_v), lut<1>(hi_ab[h], sel_v),
-                   lut<1>(lo_cd[h], sel_v), lut<1>(hi_cd[h], sel_v), pb0, pb1);
-          mma16816(acc[4 * h + 2], lut<2>(lo_ab[h], sel_v), lut<2>(hi_ab[h], sel_v),
-                   lut<2>(lo_cd[h], sel_v), lut<2>(hi_cd[h], sel_v), pb0, pb1);
-          mma16816(acc[4 * h + 3], lut<3>(lo_ab[h], sel_v), lut<3>(hi_ab[h], sel_v),
-                   lut<3>(lo_cd[h], sel_v), lut<3>(hi_cd[h], sel_v), pb0, pb1);
-        }
+        const uint32_t pb0 = movmatrix_trans(ok[u][0] ? pack_half2(p0 * nv0, p1 * nv0) : 0u);
+        const uint32_t pb1 = movmatrix_trans(ok[u][1] ? pack_half2(p2 * nv1, p3 * nv1) : 0u);
+        value_mmas<BWV, C::kVRow>(slot + C::kOffV, g, t, sel_v, pb0, pb1, acc);
       }
       __syncwarp();       // every lane is done with this half before it is refilled
     }
@@ -508,9 +646,20 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
   }
 }
 
-bool mma4_eligible(const DecodeParams &p) {
+// Worker warps per SM of the instantiation serving (bw_k, bw_v); 0 when the
+// widths have no tensor-core kernel.
+int mma_warps_per_sm(int bw_k, int bw_v) {
+  if (bw_k == 4 && bw_v == 4) return Cfg<4, 4>::kWarps;
+  if (bw_k == 4 && bw_v == 6) return Cfg<4, 6>::kWarps;
+  if (bw_k == 6 && bw_v == 6) return Cfg<6, 6>::kWarps;
+  if (bw_k == 8 && bw_v == 8) return Cfg<8, 8>::kWarps;
+  return 0;
+}
+
+bool mma_eligible(const DecodeParams &p) {
   auto aligned = [](const void *ptr) { return ((uintptr_t)ptr & 15) == 0; };
-  return p.D == 128 && p.k.bw == 4 && p.v.bw == 4 && p.S >= 16 && (p.S & (p.S - 1)) == 0 && p.n_rep <= 8 &&
+  return p.D == 128 && mma_warps_per_sm(p.k.bw, p.v.bw) > 0 && p.S >= 16 &&
+         (p.S & (p.S - 1)) == 0 && p.n_rep <= 8 &&
          aligned(p.k.pages) && aligned(p.v.pages) && aligned(p.k.norms) && aligned(p.v.norms) &&
          p.k.page_stride % 16 == 0 && p.k.head_stride % 16 == 0 && p.v.page_stride % 16 == 0 &&
          p.v.head_stride % 16 == 0 && p.k.norm_page_stride % 8 == 0 &&
@@ -518,29 +667,28 @@ bool mma4_eligible(const DecodeParams &p) {
          p.v.norm_head_stride % 8 == 0 && aligned(p.q_rot) && aligned(p.part_acc);
 }
 
-// Tokens per chunk for `splits` chunks over `max_tokens`, a multiple of 64.
-int mma4_chunk_tokens(int max_tokens, int splits) {
+// Tokens per chunk for `splits` chunks over `max_tokens`, a multiple of 32.
+int mma_chunk_tokens(int max_tokens, int splits) {
   int per = (max_tokens + splits - 1) / splits;
   per = (per + kIterTokens - 1) / kIterTokens * kIterTokens;
   return per < kIterTokens ? kIterTokens : per;
 }
 
-int launch_decode_mma4(const DecodeParams &p, const MergeParams &m, cudaStream_t stream) {
-  static int sms = 0;
-  const size_t smem = kDynamicSmem;
-  if (sms == 0) {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaFuncSetAttribute(decode_mma4_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int BWK, int BWV>
+static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cudaStream_t stream) {
+  using C = Cfg<BWK, BWV>;
+  static bool opted_in = false;
+  if (!opted_in) {
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<BWK, BWV>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)C::kDynamicSmem);
     if (e != cudaSuccess) return check_cuda(e, "wtq_decode: shared memory opt-in");
-    sms = n > 0 ? n : 148;
+    opted_in = true;
   }
   const int max_tokens = p.max_pages * p.S;
-  const int chunk_tokens = mma4_chunk_tokens(max_tokens, p.num_splits);
+  const int chunk_tokens = mma_chunk_tokens(max_tokens, p.num_splits);
   const int64_t items = (int64_t)p.B * p.Hkv * p.num_splits;
-  int grid = (int)((items + kWarps - 1) / kWarps);
+  int grid = (int)((items + C::kWarps - 1) / C::kWarps);
   if (grid > sms) grid = sms;
   // Both launches may begin before the kernel ahead of them has drained; each
   // kernel waits (griddepcontrol.wait) before it touches what that kernel wrote.
@@ -549,13 +697,13 @@ int launch_decode_mma4(const DecodeParams &p, const MergeParams &m, cudaStream_t
   pdl.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem;
+  cfg.blockDim = dim3(C::kThreads);
+  cfg.dynamicSmemBytes = C::kDynamicSmem;
   cfg.stream = stream;
   cfg.attrs = &pdl;
   cfg.numAttrs = 1;
   profile_mark_begin(stream);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma4_kernel, p, chunk_tokens);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<BWK, BWV>, p, chunk_tokens);
   profile_mark_end(stream);
   if (e != cudaSuccess) return check_cuda(e, "wtq_decode mma launch");
   cfg.gridDim = dim3((unsigned)(p.B * p.Hkv));
@@ -565,6 +713,22 @@ int launch_decode_mma4(const DecodeParams &p, const MergeParams &m, cudaStream_t
                          max_tokens);
   note_launches(2);
   return check_cuda(e, "wtq_decode merge launch");
+}
+
+int launch_decode_mma(const DecodeParams &p, const MergeParams &m, cudaStream_t stream) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sms = n > 0 ? n : 148;
+  }
+  if (p.k.bw == 4 && p.v.bw == 4) return launch_one<4, 4>(p, m, sms, stream);
+  if (p.k.bw == 4 && p.v.bw == 6) return launch_one<4, 6>(p, m, sms, stream);
+  if (p.k.bw == 6 && p.v.bw == 6) return launch_one<6, 6>(p, m, sms, stream);
+  if (p.k.bw == 8 && p.v.bw == 8) return launch_one<8, 8>(p, m, sms, stream);
+  return fail(WTQ_ERR_UNSUPPORTED, "wtq_decode: no tensor-core kernel for widths %d/%d", p.k.bw,
+              p.v.bw);
 }
 
 }  // namespace wtq
