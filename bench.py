@@ -433,7 +433,10 @@ def run_reference(args):
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "parallelism": "host cpu"},
+        "config": {"workload": f"{w.name}: B{w.batch} Hq{w.q_heads} Hkv{w.kv_heads} D{w.head_dim} "
+                               f"ctx{w.context or 'ragged'} page{w.page_size} "
+                               f"{w.bits_k}-bit K/{w.bits_v}-bit V, q {str(w.dtype)[6:]}",
+                   "parallelism": "host cpu"},
         "cpu_baseline": {"value": us, "unit": "us", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))

@@ -169,6 +169,9 @@ int wtq_dequant(const uint8_t *packed, const void *norms_f16, const float *centr
 uint64_t wtq_launch_count(void);
 int wtq_profile_enable(int capacity);
 int wtq_profile_collect(double *total_ms, int *launches);
+/* Like wtq_profile_collect, split per call into: first launch to scan start
+ * (query rotation), the scan, scan end to last launch's end (merge). */
+int wtq_profile_phases(double *before_scan_ms, double *scan_ms, double *after_scan_ms, int *calls);
 int wtq_profile_disable(void);
 
 #ifdef __cplusplus

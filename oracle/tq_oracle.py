@@ -315,6 +315,8 @@ def unpack_vectorized(packed: torch.Tensor, bit_width: int, head_dim: int) -> to
     hold stream bits [i*bw, (i+1)*bw)."""
     if bit_width == 8:
         return packed
+    if bit_width == 4:                      # byte i = code 2i | code 2i+1 << 4
+        return torch.stack((packed & 0x0F, packed >> 4), dim=-1).flatten(-2)
     nb = packed.shape[-1]
     bit = torch.arange(head_dim, dtype=torch.int64) * bit_width
     first, shift = bit // 8, (bit % 8).to(torch.int32)
@@ -327,7 +329,7 @@ def unpack_vectorized(packed: torch.Tensor, bit_width: int, head_dim: int) -> to
 
 def _codebook_rows(pages, centroids, bits, D):
     idx = unpack_vectorized(pages, bits, D)
-    return centroids[idx.long()]
+    return centroids.index_select(0, idx.reshape(-1).to(torch.int32)).view(idx.shape)
 
 
 def _history(kv: OracleKV, b: int):

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "wtq_launch_count": (ctypes.c_uint64, []),
     "wtq_profile_enable": (c_int, [c_int]),
     "wtq_profile_collect": (c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
+    "wtq_profile_phases": (c_int, [ctypes.POINTER(ctypes.c_double)] * 3 + [ctypes.POINTER(c_int)]),
     "wtq_profile_disable": (c_int, []),
     "wtq_decode_static_capacity": (c_size_t, []),
     "wtq_decode_static": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p,

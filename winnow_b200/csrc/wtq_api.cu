@@ -55,7 +55,10 @@ bool fill_side(DecodeSideDev &d, const wtq_side_t &w, int D) {
 }  // namespace
 
 extern "C" size_t wtq_decode_counter_bytes(int B, int Hkv) {
-  return round_up((size_t)(B > 0 ? B : 0) * (size_t)(Hkv > 0 ? Hkv : 0) * sizeof(int32_t), 256);
+  (void)Hkv;
+  // [0] work queue of the tensor-core scan; from byte 128 (its own cache line, so
+  // that queue traffic does not delay readers): chunk prefix, B + 1 ints
+  return round_up(128 + ((size_t)(B > 0 ? B : 0) + 1) * sizeof(int32_t), 256);
 }
 
 extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pages, int S,
@@ -66,13 +69,15 @@ extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pag
   const int warps = mma_warps_per_sm(bw_k, bw_v);
   if (D == 128 && warps > 0 && S >= 16 && (S & (S - 1)) == 0 && Hq / Hkv <= 8) {
     // tensor-core path: every warp of the persistent grid should see
-    // about three chunks, and a chunk should be long enough (>= 256 tokens)
-    // that writing its partial state stays small beside reading its pages
+    // about three chunks (upper bound: every sequence at full table width)
     const int64_t workers = (int64_t)device_sms() * warps;
     int64_t chunk = (max_tokens * groups + 3 * workers - 1) / (3 * workers);
     chunk = (chunk + 63) / 64 * 64;
+    // work is handed out dynamically, so only the tail matters: a chunk above
+    // 512 tokens would leave one warp running long after the others are done
     if (chunk < 256) chunk = 256;
-    if (chunk > 4096) chunk = 4096;
+    if (chunk > 512) chunk = 512;
+    if (chunk * kMaxSplits < max_tokens) chunk = ((max_tokens + kMaxSplits - 1) / kMaxSplits + 63) / 64 * 64;
     int64_t splits = (max_tokens + chunk - 1) / chunk;
     if (splits > kMaxSplits) splits = kMaxSplits;
     return clamp_splits((int)splits, max_pages, S);
@@ -133,6 +138,9 @@ extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], 
     return fail(WTQ_ERR_WORKSPACE, "wtq_decode: workspace %zu < %zu bytes", workspace_bytes, need);
 
   const size_t rows = (size_t)B * Hq;
+  p.work_counter = (int32_t *)workspace;
+  int32_t *chunk_prefix = (int32_t *)((char *)workspace + 128);
+  p.chunk_prefix = chunk_prefix;
   char *ws = (char *)workspace + wtq_decode_counter_bytes(B, Hkv);
   float *q_rot = (float *)ws;
   ws += round_up(rows * D * sizeof(float), 256);
@@ -156,9 +164,20 @@ extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], 
   const bool fast = mma_eligible(p) && !force_generic();
   // the tensor-core path works in the exp2 domain: fold log2(e) into the query
   const float q_scale = fast ? scale * 1.4426950408889634f : scale;
-  if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, q_scale, B, Hq, D, q_rot, stream))
+  const int max_tokens = max_pages * S;
+  m.work_counter = fast ? p.work_counter : nullptr;
+  profile_mark_call(stream, true);
+  if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, q_scale, B, Hq, D, q_rot, seq_lens,
+                               fast ? mma_chunk_tokens(max_tokens, splits) : 1, max_tokens,
+                               fast ? chunk_prefix : nullptr, stream))
     return rc;
-  if (fast) return launch_decode_mma(p, m, stream);
-  if (int rc = launch_decode_generic(p, stream)) return rc;
-  return launch_merge(m, B, stream);
+  int rc = 0;
+  if (fast) {
+    rc = launch_decode_mma(p, m, stream);
+  } else {
+    rc = launch_decode_generic(p, stream);
+    if (rc == 0) rc = launch_merge(m, B, stream);
+  }
+  profile_mark_call(stream, false);
+  return rc;
 }

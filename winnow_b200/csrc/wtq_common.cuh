@@ -22,6 +22,7 @@ void note_launches(int n);
 // wtq_profile_enable); both are no-ops while profiling is off.
 void profile_mark_begin(cudaStream_t stream);
 void profile_mark_end(cudaStream_t stream);
+void profile_mark_call(cudaStream_t stream, bool begin);
 
 inline bool width_supported(int bw) {
   return bw == 2 || bw == 3 || bw == 4 || bw == 5 || bw == 6 || bw == 8;

@@ -17,6 +17,30 @@
 
 namespace wtq {
 
+// Exclusive prefix of chunks per sequence (B + 1 ints), computed by one warp.
+__device__ void write_chunk_prefix(const int32_t *seq_lens, int B, int chunk_tokens,
+                                   int max_tokens, int32_t *chunk_prefix) {
+  int running = 0;
+  for (int b0 = 0; b0 < B; b0 += 32) {
+    const int b = b0 + (int)threadIdx.x;
+    int n = 0;
+    if (b < B) {
+      int L = seq_lens[b];
+      L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
+      n = (L + chunk_tokens - 1) / chunk_tokens;
+    }
+    int incl = n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if ((int)threadIdx.x >= o) incl += up;
+    }
+    if (b < B) chunk_prefix[b] = running + incl - n;
+    running += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (threadIdx.x == 0) chunk_prefix[B] = running;
+}
+
 // q_rot[row][c] = mult * sum_d q[row][d] Pi[c][d] for the `rows` query rows that
 // start at row blockIdx.x * NR.  A warp takes output coordinates c = warp,
 // warp + 16, ...; its lanes stride over d, so every Pi row is read once per
@@ -26,8 +50,11 @@ constexpr int kRotThreads = 512;
 template <int NR>
 __global__ void __launch_bounds__(kRotThreads) rotate_q_kernel(
     const void *q, int dtype, int64_t qsb, int64_t qsh, const float *Pi, float mult, int Hq,
-    int D, int total_rows, float *q_rot) {
+    int D, int total_rows, float *q_rot, const int32_t *seq_lens, int B, int chunk_tokens,
+    int max_tokens, int32_t *chunk_prefix) {
   __shared__ float qs[NR][256];
+  if (chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
+    write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, chunk_prefix);
   const int row0 = blockIdx.x * NR;
   for (int e = threadIdx.x; e < NR * D; e += kRotThreads) {
     const int r = e / D, d = e - r * D;
@@ -44,20 +71,25 @@ __global__ void __launch_bounds__(kRotThreads) rotate_q_kernel(
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kWarps = kRotThreads / 32, kBatch = 8;
+  // Every block needs all of Pi; blocks start at different rows so that at any
+  // moment their requests spread over all of Pi's cache lines instead of
+  // queueing on the same few.
+  const int shift = (int)((blockIdx.x * 37u) % (unsigned)D);
   for (int c0 = warp; c0 < D; c0 += kWarps * kBatch) {
     float part[kBatch][NR];
+    int rows[kBatch];
 #pragma unroll
-    for (int i = 0; i < kBatch; ++i)
+    for (int i = 0; i < kBatch; ++i) {
+      const int c = c0 + i * kWarps;
+      rows[i] = c < D ? (c + shift) % D : -1;
 #pragma unroll
       for (int r = 0; r < NR; ++r) part[i][r] = 0.f;
+    }
 #pragma unroll 4
     for (int d = lane; d < D; d += 32) {
       float w[kBatch];
 #pragma unroll
-      for (int i = 0; i < kBatch; ++i) {
-        const int c = c0 + i * kWarps;
-        w[i] = c < D ? __ldg(Pi + (int64_t)c * D + d) : 0.f;
-      }
+      for (int i = 0; i < kBatch; ++i) w[i] = rows[i] >= 0 ? __ldg(Pi + (int64_t)rows[i] * D + d) : 0.f;
 #pragma unroll
       for (int i = 0; i < kBatch; ++i)
 #pragma unroll
@@ -65,12 +97,11 @@ __global__ void __launch_bounds__(kRotThreads) rotate_q_kernel(
     }
 #pragma unroll
     for (int i = 0; i < kBatch; ++i) {
-      const int c = c0 + i * kWarps;
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
         const float v = warp_sum(part[i][r]);
-        if (lane == 0 && c < D && row0 + r < total_rows)
-          q_rot[(int64_t)(row0 + r) * D + c] = v * mult;
+        if (lane == 0 && rows[i] >= 0 && row0 + r < total_rows)
+          q_rot[(int64_t)(row0 + r) * D + rows[i]] = v * mult;
       }
     }
   }
@@ -312,15 +343,90 @@ int launch_decode_generic(const DecodeParams &p, cudaStream_t stream) {
   return check_cuda(cudaGetLastError(), "wtq_decode generic launch");
 }
 
+// Same result as rotate_q_kernel for head_dim a multiple of 16: thread
+// (column c, quarter) walks its quarter of row c of Pi with 16-byte loads (a
+// thread owns a row, so no cross-lane reduction is needed; the row's sectors
+// are reused through L1), the four query rows come from shared memory as one
+// 16-byte broadcast per coordinate, and the quarters are added through shared
+// memory.  About a seventh of the instructions of the shuffle version.
+template <int NR>
+__global__ void __launch_bounds__(kRotThreads) rotate_q_rows_kernel(
+    const void *q, int dtype, int64_t qsb, int64_t qsh, const float *Pi, float mult, int Hq,
+    int D, int total_rows, float *q_rot, const int32_t *seq_lens, int B, int chunk_tokens,
+    int max_tokens, int32_t *chunk_prefix) {
+  __shared__ __align__(16) float qs[256][NR];          // [coordinate][row]
+  __shared__ float part_s[3][NR][256];
+  const int row0 = blockIdx.x * NR;
+  if (chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
+    write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, chunk_prefix);
+  for (int e = threadIdx.x; e < NR * D; e += kRotThreads) {
+    const int r = e / D, d = e - r * D;
+    const int row = row0 + r;
+    float v = 0.f;
+    if (row < total_rows) {
+      const int b = row / Hq, h = row - b * Hq;
+      v = load_as_float(q, (int64_t)b * qsb + (int64_t)h * qsh + d, dtype);
+    }
+    qs[d][r] = v;
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  const int quarter = threadIdx.x >> 7, dq = D / 4;
+  for (int c0 = 0; c0 < D; c0 += 128) {                  // same trip count for every thread
+    const int c = c0 + (threadIdx.x & 127);
+    const bool on = c < D;
+    float acc[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+    const float4 *row = reinterpret_cast<const float4 *>(Pi + (int64_t)(on ? c : 0) * D + quarter * dq);
+    for (int j0 = 0; on && j0 < dq / 4; j0 += 8) {       // 8 loads in flight
+      float4 w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = j0 + j < dq / 4 ? __ldg(row + j0 + j) : make_float4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (j0 + j < dq / 4) {
+          const int d = quarter * dq + 4 * (j0 + j);
+          const float wv[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int r = 0; r < NR; ++r) acc[r] = fmaf(qs[d + k][r], wv[k], acc[r]);
+        }
+      }
+    }
+    if (quarter > 0 && on) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) part_s[quarter - 1][r][c] = acc[r];
+    }
+    __syncthreads();
+    if (quarter == 0 && on) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const float v = (acc[r] + part_s[0][r][c]) + (part_s[1][r][c] + part_s[2][r][c]);
+        if (row0 + r < total_rows) q_rot[(int64_t)(row0 + r) * D + c] = v * mult;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 int launch_rotate_q(const void *q, int dtype, const int64_t *qs, const float *Pi, float scale,
-                    int B, int Hq, int D, float *q_rot, cudaStream_t stream) {
+                    int B, int Hq, int D, float *q_rot, const int32_t *seq_lens, int chunk_tokens,
+                    int max_tokens, int32_t *chunk_prefix, cudaStream_t stream) {
   const int rows = B * Hq;
-  if (rows % 4 == 0)
-    rotate_q_kernel<4><<<rows / 4, kRotThreads, 0, stream>>>(q, dtype, qs[0], qs[1], Pi, scale, Hq,
-                                                            D, rows, q_rot);
+  if (D % 16 == 0 && D <= 256 && ((uintptr_t)Pi & 15) == 0)
+    rotate_q_rows_kernel<4><<<(rows + 3) / 4, kRotThreads, 0, stream>>>(
+        q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
+        max_tokens, chunk_prefix);
+  else if (rows % 4 == 0)
+    rotate_q_kernel<4><<<rows / 4, kRotThreads, 0, stream>>>(
+        q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
+        max_tokens, chunk_prefix);
   else
-    rotate_q_kernel<1><<<rows, kRotThreads, 0, stream>>>(q, dtype, qs[0], qs[1], Pi, scale, Hq, D,
-                                                        rows, q_rot);
+    rotate_q_kernel<1><<<rows, kRotThreads, 0, stream>>>(
+        q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
+        max_tokens, chunk_prefix);
   note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_decode rotate launch");
 }

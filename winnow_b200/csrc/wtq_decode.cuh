@@ -5,7 +5,7 @@
 
 namespace wtq {
 
-constexpr int kMaxSplits = 256;
+constexpr int kMaxSplits = 1024;
 
 struct DecodeSideDev {
   const uint8_t *pages;
@@ -28,6 +28,11 @@ struct DecodeParams {
   float *part_m;    // (B, Hq, splits)
   float *part_l;
   int32_t *status;
+  // tensor-core path: work queue (one int, zero between calls) and the exclusive
+  // prefix of chunks per sequence (B + 1 ints), both inside the workspace's
+  // counter block
+  int32_t *work_counter;
+  const int32_t *chunk_prefix;
 };
 
 struct MergeParams {
@@ -36,10 +41,14 @@ struct MergeParams {
   void *out;
   int64_t osb, osh;
   int dtype, Hq, D, num_splits;
+  int32_t *work_counter;   // reset to zero by the merge (null on the generic path)
 };
 
+// `chunk_prefix` (may be null): the launch also writes the exclusive prefix of
+// ceil(seq_len / chunk_tokens) over the B sequences (B + 1 ints).
 int launch_rotate_q(const void *q, int dtype, const int64_t *q_strides, const float *Pi,
-                    float scale, int B, int Hq, int D, float *q_rot, cudaStream_t stream);
+                    float scale, int B, int Hq, int D, float *q_rot, const int32_t *seq_lens,
+                    int chunk_tokens, int max_tokens, int32_t *chunk_prefix, cudaStream_t stream);
 int launch_decode_generic(const DecodeParams &p, cudaStream_t stream);
 int launch_merge(const MergeParams &p, int B, cudaStream_t stream);
 

@@ -45,7 +45,9 @@ constexpr int kTileTokens = 16;
 constexpr int kTilesPerIter = 2;                       // 32 tokens per iteration
 constexpr int kIterTokens = kTileTokens * kTilesPerIter;
 constexpr uint32_t kLutAddr = 0x10000;                 // shared address of the tables
-constexpr uint32_t kRingLow = 2048;                    // rings start here (>= dynamic smem base)
+constexpr uint32_t kPrefixAddr = 2048;                 // chunk prefix copy (>= dynamic smem base)
+constexpr int kPrefixMax = 1024;                       // entries (sequences + 1) it can hold
+constexpr uint32_t kRingLow = kPrefixAddr + 4 * kPrefixMax;   // rings start here
 constexpr uint32_t kSmemLimit = 227 * 1024;
 constexpr float kPreciseAbove = 8.0f;   // |score| (log2 units) that triggers fp32 rescoring
 
@@ -326,7 +328,7 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(dyn_smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  if (dyn_base > kRingLow) {             // layout assumption broken: refuse, do not touch memory
+  if (dyn_base > kPrefixAddr) {          // layout assumption broken: refuse, do not touch memory
     if (p.status && tid == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
     return;
   }
@@ -349,8 +351,35 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   const int S = p.S;
   const int s_shift = 31 - __clz(S);                 // S is a power of two (checked by the host)
   const int chunks = p.num_splits;
-  const int64_t items = (int64_t)p.B * p.Hkv * chunks;
-  const int workers = gridDim.x * C::kWarps;
+
+  // Exclusive prefix of chunks per sequence, in shared memory when the batch
+  // fits (it only needs seq_lens, so it too overlaps the previous kernel).
+  const bool prefix_local = p.B < kPrefixMax;
+  if (prefix_local && warp == 0) {
+    int running = 0;
+    for (int b0 = 0; b0 < p.B; b0 += 32) {
+      const int bb = b0 + lane;
+      int n = 0;
+      if (bb < p.B) {
+        int Lb = p.seq_lens[bb];
+        Lb = Lb < 0 ? 0 : (Lb > p.max_pages * p.S ? p.max_pages * p.S : Lb);
+        n = (Lb + chunk_tokens - 1) / chunk_tokens;
+      }
+      int incl = n;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (bb < p.B) sts32(kPrefixAddr + 4 * bb, (uint32_t)(running + incl - n));
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) sts32(kPrefixAddr + 4 * p.B, (uint32_t)running);
+  }
+  __syncthreads();
+  auto prefix_at = [&](int i) -> int {
+    return prefix_local ? (int)lds32(kPrefixAddr + 4 * i) : p.chunk_prefix[i];
+  };
 
   // q_rot is written by the kernel launched just before this one; everything
   // above overlapped with its tail.  The merge that follows may be scheduled as
@@ -358,12 +387,29 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
-  // Consecutive items go to different CTAs, so a last, partly filled round of
-  // items is spread over all SMs instead of filling a few of them.
-  for (int64_t item = (int64_t)warp * gridDim.x + blockIdx.x; item < items; item += workers) {
-    const int chunk = (int)(item % chunks);
-    const int kvh = (int)((item / chunks) % p.Hkv);
-    const int b = (int)(item / ((int64_t)chunks * p.Hkv));
+  // Work is handed out dynamically: item i (one chunk of one kv head of one
+  // sequence; only chunks that exist are numbered) goes to the next free warp.
+  // Every warp starts on the item with its own number (consecutive items go to
+  // different CTAs); later items come from the queue, and the next one is
+  // requested while the current one is processed, so neither the first burst
+  // of atomics nor their round trips are on the critical path.
+  const int64_t items_live = (int64_t)prefix_at(p.B) * p.Hkv;
+  const int workers = gridDim.x * C::kWarps;
+  int next_item = warp * gridDim.x + blockIdx.x;
+  for (int guard = 0; guard < (1 << 24); ++guard) {        // bounded: never spins
+    const int64_t item = __shfl_sync(0xffffffffu, next_item, 0);
+    if (item >= items_live) break;
+    if (lane == 0) next_item = workers + atomicAdd(p.work_counter, 1);
+    const int kvh = (int)(item % p.Hkv);
+    const int flat = (int)(item / p.Hkv);                   // chunk number over all sequences
+    int lo = 0, hi = p.B;                                   // last b with prefix[b] <= flat
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (prefix_at(mid) <= flat) lo = mid;
+      else hi = mid;
+    }
+    const int b = lo;
+    const int chunk = flat - prefix_at(b);
     int L = p.seq_lens[b];
     if (L > p.max_pages * S) {
       L = p.max_pages * S;
@@ -371,7 +417,7 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     }
     const int tok0 = chunk * chunk_tokens;
     const int tok1 = min(L, tok0 + chunk_tokens);
-    if (tok0 >= tok1) continue;          // the merge only visits ceil(L / chunk) chunks
+    if (tok0 >= tok1) continue;
 
     // ---- query fragments: head g, coordinates 32t .. 32t+31 ----------------
     uint32_t qf[8][2];
@@ -562,70 +608,136 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   }
 }
 
-// Merge of the chunk states of one (sequence, kv head) group and rotation of
-// its n_rep output rows back to the model basis: out = (sum_c w_c acc_c / sum_c
-// w_c l_c) Pi_V with w_c = 2^(m_c - max m).  Only the chunks that exist for
-// the sequence's length are read.  512 threads: warp w first merges head
-// w % n_rep ... (one warp per (head, quarter of the coordinates)); then thread
-// (c, part) accumulates output column c over a quarter of the rows of Pi_V for
-// every head of the group, and the four quarters are added through shared
+// Merge of the chunk states of `hpb` query heads of one (sequence, kv head)
+// group and rotation of their output rows back to the model basis:
+// out = (sum_c w_c acc_c / sum_c w_c l_c) Pi_V with w_c = 2^(m_c - max m).  Only
+// the chunks that exist for the sequence's length are read.  grid = (groups,
+// n_rep / hpb): few groups with many chunks (one long sequence) are spread over
+// more blocks by giving each block fewer heads.  512 threads: one warp per head
+// computes the weights; the chunk sum of a (head, coordinate) is split over
+// 512 / (hpb * 128) threads; thread (column, quarter) accumulates its quarter of
+// the rows of Pi_V for every head, and the quarters are added through shared
 // memory.
 constexpr int kMergeThreads = 512;
 __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
-    MergeParams p, const int32_t *seq_lens, int Hkv, int n_rep, int chunk_tokens, int max_tokens) {
-  __shared__ float a_s[8][128];
-  __shared__ float w_s[8][kMaxSplits];
+    MergeParams p, const int32_t *seq_lens, int Hkv, int n_rep, int hpb, int chunk_tokens,
+    int max_tokens) {
+  __shared__ float a_s[8][128];           // [way * hpb + head][coordinate] partial chunk sums
+  __shared__ float w_s[8][kMaxSplits];    // chunk weights; reused for the rotation's partial sums
   __shared__ float inv_s[8];
-  __shared__ float o_s[4][8][128];
   const int b = blockIdx.x / Hkv, kvh = blockIdx.x - b * Hkv;
+  const int head0 = kvh * n_rep + blockIdx.y * hpb;          // first query head of this block
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Pi_V does not depend on the scan: fetch this thread's 32 elements while the
   // scan kernel is still draining.
   const int col = tid & 127, part = tid >> 7;
   float wv[32];
+  // (rows are visited in an order that differs from block to block, so the
+  // blocks' requests spread over Pi_V's cache lines)
+  const int turn = (int)(blockIdx.x * 5u + blockIdx.y * 3u) & 31;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) wv[i] = __ldg(p.Pi_v + (part * 32 + i) * 128 + col);
+  for (int i = 0; i < 32; ++i) wv[i] = __ldg(p.Pi_v + (part * 32 + ((i + turn) & 31)) * 128 + col);
   asm volatile("griddepcontrol.wait;\n" ::: "memory");      // partial states are complete
+  if (p.work_counter != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
+    *p.work_counter = 0;
   int L = seq_lens[b];
   L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
   const int chunks = (L + chunk_tokens - 1) / chunk_tokens;
-  const int64_t row0 = ((int64_t)b * p.Hq + kvh * n_rep) * p.num_splits;
-  if (warp < n_rep) {                                  // weights of head `warp`
+  const int64_t row0 = ((int64_t)b * p.Hq + head0) * p.num_splits;
+  // The first 32 chunk states of this thread's (head, coordinate) are requested
+  // now, so that their round trip overlaps the one of the weights below.
+  const int ways = hpb <= 1 ? 4 : hpb <= 2 ? 2 : 1;        // threads sharing one (head, coordinate)
+  const int e0 = tid;                                      // first (and for hpb <= 4 only) element
+  const bool e0_on = e0 < hpb * 128 * ways;
+  const int way0 = e0 / (hpb * 128), hd0 = e0 - way0 * hpb * 128;
+  const float *src0 = p.part_acc + (row0 + (int64_t)(hd0 >> 7) * p.num_splits) * 128 + (hd0 & 127);
+  float v0[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int c = way0 + i * ways;
+    v0[i] = e0_on && c < chunks ? __ldcg(src0 + (int64_t)c * 128) : 0.f;
+  }
+  if (warp < hpb) {                                    // weights of head `warp`
     const int64_t base = row0 + (int64_t)warp * p.num_splits;
-    // up to 8 chunks per lane (256 chunks at most), m and l fetched together
-    float mv[8], lv[8], gmax = -INFINITY;
+    float gmax = -INFINITY, denom = 0.f;
+    if (chunks <= 256) {                               // one round trip: 8 chunks per lane
+      float mv[8], lv[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = lane + 32 * i;
-      mv[i] = c < chunks ? __ldcg(p.part_m + base + c) : -INFINITY;
-      lv[i] = c < chunks ? __ldcg(p.part_l + base + c) : 0.f;
-    }
+      for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        mv[i] = c < chunks ? __ldcg(p.part_m + base + c) : -INFINITY;
+        lv[i] = c < chunks ? __ldcg(p.part_l + base + c) : 0.f;
+      }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) gmax = fmaxf(gmax, mv[i]);
-    gmax = warp_max(gmax);
-    float denom = 0.f;
+      for (int i = 0; i < 8; ++i) gmax = fmaxf(gmax, mv[i]);
+      gmax = warp_max(gmax);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = lane + 32 * i;
-      const float w = mv[i] == -INFINITY ? 0.f : exp2f(mv[i] - gmax);
-      if (c < chunks) w_s[warp][c] = w;
-      denom += w * lv[i];
+      for (int i = 0; i < 8; ++i) {
+        const int c = lane + 32 * i;
+        const float w = mv[i] == -INFINITY ? 0.f : exp2f(mv[i] - gmax);
+        if (c < chunks) w_s[warp][c] = w;
+        denom += w * lv[i];
+      }
+    } else {
+      for (int c0 = 0; c0 < chunks; c0 += 256) {       // 8 loads per lane in flight
+        float mv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = c0 + lane + 32 * i;
+          mv[i] = c < chunks ? __ldcg(p.part_m + base + c) : -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gmax = fmaxf(gmax, mv[i]);
+      }
+      gmax = warp_max(gmax);
+      for (int c0 = 0; c0 < chunks; c0 += 256) {
+        float mv[8], lv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = c0 + lane + 32 * i;
+          mv[i] = c < chunks ? __ldcg(p.part_m + base + c) : -INFINITY;
+          lv[i] = c < chunks ? __ldcg(p.part_l + base + c) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = c0 + lane + 32 * i;
+          const float w = mv[i] == -INFINITY ? 0.f : exp2f(mv[i] - gmax);
+          if (c < chunks) w_s[warp][c] = w;
+          denom += w * lv[i];
+        }
+      }
     }
     denom = warp_sum(denom);
     if (lane == 0) inv_s[warp] = denom > 0.f ? 1.f / fmaxf(denom, 1e-30f) : 0.f;
   }
   __syncthreads();
-  for (int e = tid; e < n_rep * 128; e += kMergeThreads) {
-    const int h = e >> 7, d = e & 127;
+  // chunk sums
+  for (int e = tid; e < hpb * 128 * ways; e += kMergeThreads) {
+    const int way = e / (hpb * 128), hd = e - way * hpb * 128;
+    const int h = hd >> 7, d = hd & 127;
     const float *src = p.part_acc + (row0 + (int64_t)h * p.num_splits) * 128 + d;
     float a = 0.f;
-    for (int c0 = 0; c0 < chunks; c0 += 32) {              // 32 loads in flight
+    for (int c0 = way; c0 < chunks; c0 += 32 * ways) {      // 32 loads in flight
       float v[32];
+      const bool preloaded = e == tid && c0 == way;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = c0 + i < chunks ? __ldcg(src + (int64_t)(c0 + i) * 128) : 0.f;
+      for (int i = 0; i < 32; ++i) {
+        const int c = c0 + i * ways;
+        v[i] = preloaded ? v0[i] : (c < chunks ? __ldcg(src + (int64_t)c * 128) : 0.f);
+      }
 #pragma unroll
-      for (int i = 0; i < 32; ++i) a = fmaf(c0 + i < chunks ? w_s[h][c0 + i] : 0.f, v[i], a);
+      for (int i = 0; i < 32; ++i) {
+        const int c = c0 + i * ways;
+        a = fmaf(c < chunks ? w_s[h][c] : 0.f, v[i], a);
+      }
     }
+    a_s[way * hpb + h][d] = a;
+  }
+  __syncthreads();
+  for (int e = tid; e < hpb * 128; e += kMergeThreads) {
+    const int h = e >> 7, d = e & 127;
+    float a = a_s[h][d];
+    for (int w = 1; w < ways; ++w) a += a_s[w * hpb + h][d];
     a_s[h][d] = a * inv_s[h];
   }
   __syncthreads();
@@ -635,14 +747,25 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
 #pragma unroll
   for (int i = 0; i < 32; ++i)
 #pragma unroll
-    for (int h = 0; h < 8; ++h) o[h] = fmaf(a_s[h][part * 32 + i], wv[i], o[h]);
+    for (int h = 0; h < 8; ++h)
+      o[h] = fmaf(h < hpb ? a_s[h][part * 32 + ((i + turn) & 31)] : 0.f, wv[i], o[h]);
+  // the weights are consumed (second barrier above): their storage now holds the
+  // partial outputs of quarters 1..3; quarter 0 stays in registers
+  float (*o_s)[8][128] = reinterpret_cast<float (*)[8][128]>(&w_s[0][0]);
+  if (part > 0) {
 #pragma unroll
-  for (int h = 0; h < 8; ++h) o_s[part][h][col] = o[h];
+    for (int h = 0; h < 8; ++h) o_s[part][h][col] = o[h];
+  }
   __syncthreads();
-  for (int e = tid; e < n_rep * 128; e += kMergeThreads) {
-    const int h = e >> 7, c = e & 127;
-    const float v = (o_s[0][h][c] + o_s[1][h][c]) + (o_s[2][h][c] + o_s[3][h][c]);
-    store_from_float(p.out, (int64_t)b * p.osb + (int64_t)(kvh * n_rep + h) * p.osh + c, v, p.dtype);
+  if (part == 0) {
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+      if (h < hpb) {
+        const float v = (o[h] + o_s[1][h][col]) + (o_s[2][h][col] + o_s[3][h][col]);
+        store_from_float(p.out, (int64_t)b * p.osb + (int64_t)(head0 + h) * p.osh + col, v,
+                         p.dtype);
+      }
+    }
   }
 }
 
@@ -706,11 +829,15 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
   cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<BWK, BWV>, p, chunk_tokens);
   profile_mark_end(stream);
   if (e != cudaSuccess) return check_cuda(e, "wtq_decode mma launch");
-  cfg.gridDim = dim3((unsigned)(p.B * p.Hkv));
+  // heads per merge block: all of the group when there are many groups, fewer
+  // (down to one) when a handful of long sequences would leave most SMs idle
+  int hpb = p.n_rep;
+  while (hpb > 1 && hpb % 2 == 0 && (int64_t)p.B * p.Hkv * (p.n_rep / hpb) < sms / 2) hpb /= 2;
+  cfg.gridDim = dim3((unsigned)(p.B * p.Hkv), (unsigned)(p.n_rep / hpb));
   cfg.blockDim = dim3(kMergeThreads);
   cfg.dynamicSmemBytes = 0;
-  e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, p.seq_lens, p.Hkv, p.n_rep, chunk_tokens,
-                         max_tokens);
+  e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, p.seq_lens, p.Hkv, p.n_rep, hpb,
+                         chunk_tokens, max_tokens);
   note_launches(2);
   return check_cuda(e, "wtq_decode merge launch");
 }

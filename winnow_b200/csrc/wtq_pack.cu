@@ -49,7 +49,22 @@ void profile_mark_end(cudaStream_t stream) {
     g_open = false;
   }
 }
+// Call boundaries (before the first and after the last launch of a wtq_decode
+// call), recorded alongside the scan's pair.
+static std::vector<cudaEvent_t> g_call_begin, g_call_end;
+void profile_mark_call(cudaStream_t stream, bool begin) {
+  std::lock_guard<std::mutex> hold(g_profile_lock);
+  if (begin) {
+    if (g_recorded < (int)g_call_begin.size() && !g_open) cudaEventRecord(g_call_begin[g_recorded], stream);
+  } else if (g_recorded > 0 && g_recorded <= (int)g_call_end.size()) {
+    cudaEventRecord(g_call_end[g_recorded - 1], stream);
+  }
+}
 static void profile_release() {
+  for (cudaEvent_t e : g_call_begin) cudaEventDestroy(e);
+  for (cudaEvent_t e : g_call_end) cudaEventDestroy(e);
+  g_call_begin.clear();
+  g_call_end.clear();
   for (cudaEvent_t e : g_begin) cudaEventDestroy(e);
   for (cudaEvent_t e : g_end) cudaEventDestroy(e);
   g_begin.clear();
@@ -117,6 +132,13 @@ extern "C" int wtq_profile_enable(int capacity) {
     }
     g_begin.push_back(b);
     g_end.push_back(e);
+    cudaEvent_t cb, ce;
+    if (cudaEventCreate(&cb) != cudaSuccess || cudaEventCreate(&ce) != cudaSuccess) {
+      profile_release();
+      return check_cuda(cudaGetLastError(), "wtq_profile_enable");
+    }
+    g_call_begin.push_back(cb);
+    g_call_end.push_back(ce);
   }
   return WTQ_OK;
 }
@@ -134,6 +156,26 @@ extern "C" int wtq_profile_collect(double *total_ms, int *launches) {
   }
   *total_ms = sum;
   *launches = g_recorded;
+  g_recorded = 0;
+  return WTQ_OK;
+}
+
+extern "C" int wtq_profile_phases(double *before_scan_ms, double *scan_ms, double *after_scan_ms,
+                                  int *calls) {
+  if (!before_scan_ms || !scan_ms || !after_scan_ms || !calls)
+    return fail(WTQ_ERR_ARG, "wtq_profile_phases: null output");
+  std::lock_guard<std::mutex> hold(g_profile_lock);
+  double a = 0.0, b = 0.0, c = 0.0;
+  for (int i = 0; i < g_recorded; ++i) {
+    float t0 = 0.f, t1 = 0.f, t2 = 0.f;
+    cudaError_t e = cudaEventSynchronize(g_call_end[i]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t0, g_call_begin[i], g_begin[i]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t1, g_begin[i], g_end[i]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&t2, g_end[i], g_call_end[i]);
+    if (e != cudaSuccess) return check_cuda(e, "wtq_profile_phases");
+    a += t0; b += t1; c += t2;
+  }
+  *before_scan_ms = a; *scan_ms = b; *after_scan_ms = c; *calls = g_recorded;
   g_recorded = 0;
   return WTQ_OK;
 }
