@@ -13,6 +13,8 @@
 // Follows the schedule of the reference's tiled operator
 // (turboquant_kv/packed_attention.py:260-334) and its split merge
 // (turboquant_kv/packed_attention_triton.py:137-159); all state is fp32.
+#include <algorithm>
+
 #include "wtq_decode.cuh"
 
 namespace wtq {
@@ -356,58 +358,71 @@ __global__ void __launch_bounds__(kRotThreads) rotate_q_rows_kernel(
     int max_tokens, int32_t *chunk_prefix) {
   __shared__ __align__(16) float qs[256][NR];          // [coordinate][row]
   __shared__ float part_s[3][NR][256];
-  const int row0 = blockIdx.x * NR;
   if (chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
     write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, chunk_prefix);
-  for (int e = threadIdx.x; e < NR * D; e += kRotThreads) {
-    const int r = e / D, d = e - r * D;
-    const int row = row0 + r;
-    float v = 0.f;
-    if (row < total_rows) {
-      const int b = row / Hq, h = row - b * Hq;
-      v = load_as_float(q, (int64_t)b * qsb + (int64_t)h * qsh + d, dtype);
-    }
-    qs[d][r] = v;
+  const int quarter = threadIdx.x >> 7, dq = D / 4, col = threadIdx.x & 127;
+  // For head_dim <= 128 a thread's share of Pi (a quarter of one row, at most 8
+  // float4) stays in registers for every group of rows this block processes.
+  const bool resident = D <= 128;
+  float4 held[8];
+  if (resident) {
+    const float4 *row = reinterpret_cast<const float4 *>(Pi + (int64_t)(col < D ? col : 0) * D + quarter * dq);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) held[j] = (col < D && j < dq / 4) ? __ldg(row + j) : make_float4(0, 0, 0, 0);
   }
-  __syncthreads();
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-  const int quarter = threadIdx.x >> 7, dq = D / 4;
-  for (int c0 = 0; c0 < D; c0 += 128) {                  // same trip count for every thread
-    const int c = c0 + (threadIdx.x & 127);
-    const bool on = c < D;
-    float acc[NR];
+  const int groups = (total_rows + NR - 1) / NR;
+  for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+    const int row0 = grp * NR;
+    for (int e = threadIdx.x; e < NR * D; e += kRotThreads) {
+      const int r = e / D, d = e - r * D;
+      const int row = row0 + r;
+      float v = 0.f;
+      if (row < total_rows) {
+        const int b = row / Hq, h = row - b * Hq;
+        v = load_as_float(q, (int64_t)b * qsb + (int64_t)h * qsh + d, dtype);
+      }
+      qs[d][r] = v;
+    }
+    __syncthreads();
+    if (grp == (int)blockIdx.x) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    for (int c0 = 0; c0 < D; c0 += 128) {                  // same trip count for every thread
+      const int c = c0 + col;
+      const bool on = c < D;
+      float acc[NR];
 #pragma unroll
-    for (int r = 0; r < NR; ++r) acc[r] = 0.f;
-    const float4 *row = reinterpret_cast<const float4 *>(Pi + (int64_t)(on ? c : 0) * D + quarter * dq);
-    for (int j0 = 0; on && j0 < dq / 4; j0 += 8) {       // 8 loads in flight
-      float4 w[8];
+      for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+      const float4 *row = reinterpret_cast<const float4 *>(Pi + (int64_t)(on ? c : 0) * D + quarter * dq);
+      for (int j0 = 0; on && j0 < dq / 4; j0 += 8) {       // 8 loads in flight
+        float4 w[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) w[j] = j0 + j < dq / 4 ? __ldg(row + j0 + j) : make_float4(0, 0, 0, 0);
+        for (int j = 0; j < 8; ++j)
+          w[j] = resident ? held[j] : (j0 + j < dq / 4 ? __ldg(row + j0 + j) : make_float4(0, 0, 0, 0));
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (j0 + j < dq / 4) {
-          const int d = quarter * dq + 4 * (j0 + j);
-          const float wv[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+        for (int j = 0; j < 8; ++j) {
+          if (j0 + j < dq / 4) {
+            const int d = quarter * dq + 4 * (j0 + j);
+            const float wv[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
+            for (int k = 0; k < 4; ++k)
 #pragma unroll
-            for (int r = 0; r < NR; ++r) acc[r] = fmaf(qs[d + k][r], wv[k], acc[r]);
+              for (int r = 0; r < NR; ++r) acc[r] = fmaf(qs[d + k][r], wv[k], acc[r]);
+          }
         }
       }
-    }
-    if (quarter > 0 && on) {
+      if (quarter > 0 && on) {
 #pragma unroll
-      for (int r = 0; r < NR; ++r) part_s[quarter - 1][r][c] = acc[r];
-    }
-    __syncthreads();
-    if (quarter == 0 && on) {
-#pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        const float v = (acc[r] + part_s[0][r][c]) + (part_s[1][r][c] + part_s[2][r][c]);
-        if (row0 + r < total_rows) q_rot[(int64_t)(row0 + r) * D + c] = v * mult;
+        for (int r = 0; r < NR; ++r) part_s[quarter - 1][r][c] = acc[r];
       }
+      __syncthreads();
+      if (quarter == 0 && on) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          const float v = (acc[r] + part_s[0][r][c]) + (part_s[1][r][c] + part_s[2][r][c]);
+          if (row0 + r < total_rows) q_rot[(int64_t)(row0 + r) * D + c] = v * mult;
+        }
+      }
+      __syncthreads();
     }
-    __syncthreads();
   }
 }
 
@@ -416,7 +431,7 @@ int launch_rotate_q(const void *q, int dtype, const int64_t *qs, const float *Pi
                     int max_tokens, int32_t *chunk_prefix, cudaStream_t stream) {
   const int rows = B * Hq;
   if (D % 16 == 0 && D <= 256 && ((uintptr_t)Pi & 15) == 0)
-    rotate_q_rows_kernel<4><<<(rows + 3) / 4, kRotThreads, 0, stream>>>(
+    rotate_q_rows_kernel<4><<<std::min((rows + 3) / 4, 2 * 148), kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
         max_tokens, chunk_prefix);
   else if (rows % 4 == 0)

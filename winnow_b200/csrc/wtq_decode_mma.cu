@@ -33,6 +33,7 @@
 //
 // Reference schedule being reproduced: turboquant_kv/packed_attention.py:
 // 260-334 (tiled online softmax), split merge :328-334.
+#include <algorithm>
 #include <type_traits>
 
 #include "wtq_decode.cuh"
@@ -390,16 +391,15 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   // Work is handed out dynamically: item i (one chunk of one kv head of one
   // sequence; only chunks that exist are numbered) goes to the next free warp.
   // Every warp starts on the item with its own number (consecutive items go to
-  // different CTAs); later items come from the queue, and the next one is
-  // requested while the current one is processed, so neither the first burst
-  // of atomics nor their round trips are on the critical path.
+  // different CTAs); later items come from the queue.  The next item is
+  // requested one window before the current one ends: its round trip is hidden
+  // and the requests of different warps are spread in time.
   const int64_t items_live = (int64_t)prefix_at(p.B) * p.Hkv;
   const int workers = gridDim.x * C::kWarps;
   int next_item = warp * gridDim.x + blockIdx.x;
   for (int guard = 0; guard < (1 << 24); ++guard) {        // bounded: never spins
     const int64_t item = __shfl_sync(0xffffffffu, next_item, 0);
     if (item >= items_live) break;
-    if (lane == 0) next_item = workers + atomicAdd(p.work_counter, 1);
     const int kvh = (int)(item % p.Hkv);
     const int flat = (int)(item / p.Hkv);                   // chunk number over all sequences
     int lo = 0, hi = p.B;                                   // last b with prefix[b] <= flat
@@ -417,7 +417,10 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     }
     const int tok0 = chunk * chunk_tokens;
     const int tok1 = min(L, tok0 + chunk_tokens);
-    if (tok0 >= tok1) continue;
+    if (tok0 >= tok1) {                  // cannot happen with a consistent prefix; stay safe
+      if (lane == 0) next_item = workers + atomicAdd(p.work_counter, 1);
+      continue;
+    }
 
     // ---- query fragments: head g, coordinates 32t .. 32t+31 ----------------
     uint32_t qf[8][2];
@@ -491,6 +494,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     uint32_t loaded_next = issue(0, 0);
     for (int it = 0; it < n_iter; ++it) {
       const int buf = it & 1;
+      if (it == (n_iter > 1 ? n_iter - 2 : 0) && lane == 0)
+        next_item = workers + atomicAdd(p.work_counter, 1);
       const uint32_t loaded = loaded_next;
       loaded_next = issue(it + 1, buf ^ 1);
       cp_async_wait<1>();
@@ -619,44 +624,59 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
 // the rows of Pi_V for every head, and the quarters are added through shared
 // memory.
 constexpr int kMergeThreads = 512;
-__global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
-    MergeParams p, const int32_t *seq_lens, int Hkv, int n_rep, int hpb, int chunk_tokens,
-    int max_tokens) {
+__global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
+    MergeParams p, const int32_t *seq_lens, int num_groups, int Hkv, int n_rep, int hpb,
+    int chunk_tokens, int max_tokens) {
   __shared__ float a_s[8][128];           // [way * hpb + head][coordinate] partial chunk sums
   __shared__ float w_s[8][kMaxSplits];    // chunk weights; reused for the rotation's partial sums
   __shared__ float inv_s[8];
-  const int b = blockIdx.x / Hkv, kvh = blockIdx.x - b * Hkv;
-  const int head0 = kvh * n_rep + blockIdx.y * hpb;          // first query head of this block
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // Pi_V does not depend on the scan: fetch this thread's 32 elements while the
-  // scan kernel is still draining.
+  // Pi_V does not depend on the scan: stage it in shared memory while the scan
+  // kernel is still draining; it serves every group this block merges.
+  extern __shared__ __align__(16) float pi_s[];            // [128][128]
   const int col = tid & 127, part = tid >> 7;
-  float wv[32];
-  // (rows are visited in an order that differs from block to block, so the
-  // blocks' requests spread over Pi_V's cache lines)
-  const int turn = (int)(blockIdx.x * 5u + blockIdx.y * 3u) & 31;
+  {
+    const float4 *src = reinterpret_cast<const float4 *>(p.Pi_v);
+    float4 *dst = reinterpret_cast<float4 *>(pi_s);
+    const int shift = (int)((blockIdx.x * 37u + blockIdx.y * 11u) & 7u) * 512;   // spread the blocks
 #pragma unroll
-  for (int i = 0; i < 32; ++i) wv[i] = __ldg(p.Pi_v + (part * 32 + ((i + turn) & 31)) * 128 + col);
+    for (int i = 0; i < 8; ++i) {
+      const int e = (tid + i * kMergeThreads + shift) & 4095;
+      dst[e] = __ldg(src + e);
+    }
+  }
   asm volatile("griddepcontrol.wait;\n" ::: "memory");      // partial states are complete
   if (p.work_counter != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
     *p.work_counter = 0;
+  // The first 32 chunk states of a thread's (head, coordinate) are requested one
+  // group ahead: for the first group before its weights, for every later group
+  // during the previous group's rotation, so their round trip is hidden.
+  const int ways = hpb <= 1 ? 4 : hpb <= 2 ? 2 : 1;        // threads sharing one (head, coordinate)
+  const bool e0_on = tid < hpb * 128 * ways;               // element `tid` exists
+  const int way0 = tid / (hpb * 128), hd0 = tid - way0 * hpb * 128;
+  float v0[32];
+  auto preload = [&](int grp) {
+    const int gb = grp / Hkv, gk = grp - gb * Hkv;
+    int gl = seq_lens[gb];
+    gl = gl < 0 ? 0 : (gl > max_tokens ? max_tokens : gl);
+    const int gchunks = (gl + chunk_tokens - 1) / chunk_tokens;
+    const float *src0 = p.part_acc +
+        (((int64_t)gb * p.Hq + gk * n_rep + blockIdx.y * hpb + (hd0 >> 7)) * p.num_splits) * 128 +
+        (hd0 & 127);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int c = way0 + i * ways;
+      v0[i] = e0_on && c < gchunks ? __ldcg(src0 + (int64_t)c * 128) : 0.f;
+    }
+  };
+  if ((int)blockIdx.x < num_groups) preload(blockIdx.x);
+  for (int group = blockIdx.x; group < num_groups; group += gridDim.x) {
+  const int b = group / Hkv, kvh = group - b * Hkv;
+  const int head0 = kvh * n_rep + blockIdx.y * hpb;          // first query head of this pass
   int L = seq_lens[b];
   L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
   const int chunks = (L + chunk_tokens - 1) / chunk_tokens;
   const int64_t row0 = ((int64_t)b * p.Hq + head0) * p.num_splits;
-  // The first 32 chunk states of this thread's (head, coordinate) are requested
-  // now, so that their round trip overlaps the one of the weights below.
-  const int ways = hpb <= 1 ? 4 : hpb <= 2 ? 2 : 1;        // threads sharing one (head, coordinate)
-  const int e0 = tid;                                      // first (and for hpb <= 4 only) element
-  const bool e0_on = e0 < hpb * 128 * ways;
-  const int way0 = e0 / (hpb * 128), hd0 = e0 - way0 * hpb * 128;
-  const float *src0 = p.part_acc + (row0 + (int64_t)(hd0 >> 7) * p.num_splits) * 128 + (hd0 & 127);
-  float v0[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const int c = way0 + i * ways;
-    v0[i] = e0_on && c < chunks ? __ldcg(src0 + (int64_t)c * 128) : 0.f;
-  }
   if (warp < hpb) {                                    // weights of head `warp`
     const int64_t base = row0 + (int64_t)warp * p.num_splits;
     float gmax = -INFINITY, denom = 0.f;
@@ -711,24 +731,25 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
     if (lane == 0) inv_s[warp] = denom > 0.f ? 1.f / fmaxf(denom, 1e-30f) : 0.f;
   }
   __syncthreads();
-  // chunk sums
+  // chunk sums: element `tid` starts from the states requested above; a group of
+  // 8 heads has a second element per thread
   for (int e = tid; e < hpb * 128 * ways; e += kMergeThreads) {
     const int way = e / (hpb * 128), hd = e - way * hpb * 128;
     const int h = hd >> 7, d = hd & 127;
     const float *src = p.part_acc + (row0 + (int64_t)h * p.num_splits) * 128 + d;
     float a = 0.f;
     for (int c0 = way; c0 < chunks; c0 += 32 * ways) {      // 32 loads in flight
-      float v[32];
-      const bool preloaded = e == tid && c0 == way;
+      if (e != tid || c0 != way) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int c = c0 + i * ways;
-        v[i] = preloaded ? v0[i] : (c < chunks ? __ldcg(src + (int64_t)c * 128) : 0.f);
+        for (int i = 0; i < 32; ++i) {
+          const int c = c0 + i * ways;
+          v0[i] = c < chunks ? __ldcg(src + (int64_t)c * 128) : 0.f;
+        }
       }
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const int c = c0 + i * ways;
-        a = fmaf(c < chunks ? w_s[h][c] : 0.f, v[i], a);
+        a = fmaf(c < chunks ? w_s[h][c] : 0.f, v0[i], a);
       }
     }
     a_s[way * hpb + h][d] = a;
@@ -741,6 +762,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
     a_s[h][d] = a * inv_s[h];
   }
   __syncthreads();
+  if (group + (int)gridDim.x < num_groups) preload(group + gridDim.x);   // next group's states
   float o[8];
 #pragma unroll
   for (int h = 0; h < 8; ++h) o[h] = 0.f;
@@ -748,7 +770,7 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
   for (int i = 0; i < 32; ++i)
 #pragma unroll
     for (int h = 0; h < 8; ++h)
-      o[h] = fmaf(h < hpb ? a_s[h][part * 32 + ((i + turn) & 31)] : 0.f, wv[i], o[h]);
+      o[h] = fmaf(h < hpb ? a_s[h][part * 32 + i] : 0.f, pi_s[(part * 32 + i) * 128 + col], o[h]);
   // the weights are consumed (second barrier above): their storage now holds the
   // partial outputs of quarters 1..3; quarter 0 stays in registers
   float (*o_s)[8][128] = reinterpret_cast<float (*)[8][128]>(&w_s[0][0]);
@@ -766,6 +788,8 @@ __global__ void __launch_bounds__(kMergeThreads) merge_group_kernel(
                          p.dtype);
       }
     }
+  }
+  __syncthreads();                        // shared arrays are reused by the next group
   }
 }
 
@@ -806,6 +830,9 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)C::kDynamicSmem);
     if (e != cudaSuccess) return check_cuda(e, "wtq_decode: shared memory opt-in");
+    e = cudaFuncSetAttribute(merge_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             128 * 128 * (int)sizeof(float));
+    if (e != cudaSuccess) return check_cuda(e, "wtq_decode: merge shared memory opt-in");
     opted_in = true;
   }
   const int max_tokens = p.max_pages * p.S;
@@ -833,10 +860,11 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
   // (down to one) when a handful of long sequences would leave most SMs idle
   int hpb = p.n_rep;
   while (hpb > 1 && hpb % 2 == 0 && (int64_t)p.B * p.Hkv * (p.n_rep / hpb) < sms / 2) hpb /= 2;
-  cfg.gridDim = dim3((unsigned)(p.B * p.Hkv), (unsigned)(p.n_rep / hpb));
+  const int num_groups = p.B * p.Hkv;
+  cfg.gridDim = dim3((unsigned)std::min(num_groups, 2 * sms), (unsigned)(p.n_rep / hpb));
   cfg.blockDim = dim3(kMergeThreads);
-  cfg.dynamicSmemBytes = 0;
-  e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, p.seq_lens, p.Hkv, p.n_rep, hpb,
+  cfg.dynamicSmemBytes = 128 * 128 * sizeof(float);
+  e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, p.seq_lens, num_groups, p.Hkv, p.n_rep, hpb,
                          chunk_tokens, max_tokens);
   note_launches(2);
   return check_cuda(e, "wtq_decode merge launch");
