@@ -232,3 +232,28 @@ def test_append_then_decode_through_the_cache():
     okv = orc.OracleKV(kp, kn, vp, vn, table, torch.tensor([L + 1 for L in lens], dtype=torch.int32),
                        oq.Pi, oq.centroids, 4, ov.Pi, ov.centroids, 6, D)
     assert_attention_close(out.transpose(1, 2), orc.tiled_attention(q, okv, D ** -0.5))
+
+
+def test_repeated_calls_reuse_the_marshalled_plan():
+    """Same buffers, page ids vouched for: the second call takes the remembered
+    plan, sees data updated in place, and still matches the oracle."""
+    from winnow_b200 import packed_attention_cuda as pac
+    c = cases.AttnCase("plan", 31, 2, 8, 2, 128, (70, 33), 16, 4, 4)
+    q, okv, _ = oracle_case(c)
+    kv = to_device(okv, DEV)
+    scale = orc.default_scale(128)
+    qd = q.to(DEV)
+    out = torch.empty_like(qd)
+    ws = pac.decode_workspace(2, 8, 2, 128, kv.page_table.shape[1], 16, 0, DEV)
+    pac._PLANS.clear()
+    first = packed_decode_attention(qd, kv, scale, out=out, workspace=ws, check_page_ids=False).clone()
+    assert len(pac._PLANS) == 1
+    q2 = torch.randn(q.shape, generator=torch.Generator().manual_seed(5))
+    qd.copy_(q2)                                         # new query, same buffer
+    second = packed_decode_attention(qd, kv, scale, out=out, workspace=ws, check_page_ids=False)
+    assert len(pac._PLANS) == 1 and second.data_ptr() == out.data_ptr()
+    assert_attention_close(first, orc.tiled_attention(q, okv, scale))
+    assert_attention_close(second, orc.tiled_attention(q2, okv, scale))
+    # a checked call never uses the cache
+    packed_decode_attention(qd, kv, scale, out=out, workspace=ws)
+    assert len(pac._PLANS) == 1

@@ -355,9 +355,9 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
 
   // Exclusive prefix of chunks per sequence, in shared memory when the batch
   // fits (it only needs seq_lens, so it too overlaps the previous kernel).
-  const bool prefix_local = p.B < kPrefixMax;
+  const bool prefix_local = p.B < kPrefixMax - 1;
   if (prefix_local && warp == 0) {
-    int running = 0;
+    int running = 0, least = 0x7fffffff, most = 0;
     for (int b0 = 0; b0 < p.B; b0 += 32) {
       const int bb = b0 + lane;
       int n = 0;
@@ -365,6 +365,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
         int Lb = p.seq_lens[bb];
         Lb = Lb < 0 ? 0 : (Lb > p.max_pages * p.S ? p.max_pages * p.S : Lb);
         n = (Lb + chunk_tokens - 1) / chunk_tokens;
+        least = min(least, n);
+        most = max(most, n);
       }
       int incl = n;
 #pragma unroll
@@ -376,6 +378,14 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
       running += __shfl_sync(0xffffffffu, incl, 31);
     }
     if (lane == 0) sts32(kPrefixAddr + 4 * p.B, (uint32_t)running);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      least = min(least, __shfl_xor_sync(0xffffffffu, least, o));
+      most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
+    }
+    // all sequences have the same number of chunks: items are equal, a fixed
+    // round-robin balances them and the queue is not needed
+    if (lane == 0) sts32(kPrefixAddr + 4 * (kPrefixMax - 1), least == most ? 1u : 0u);
   }
   __syncthreads();
   auto prefix_at = [&](int i) -> int {
@@ -396,6 +406,7 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   // and the requests of different warps are spread in time.
   const int64_t items_live = (int64_t)prefix_at(p.B) * p.Hkv;
   const int workers = gridDim.x * C::kWarps;
+  const bool fixed_rounds = prefix_local && lds32(kPrefixAddr + 4 * (kPrefixMax - 1)) != 0u;
   int next_item = warp * gridDim.x + blockIdx.x;
   for (int guard = 0; guard < (1 << 24); ++guard) {        // bounded: never spins
     const int64_t item = __shfl_sync(0xffffffffu, next_item, 0);
@@ -418,7 +429,7 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     const int tok0 = chunk * chunk_tokens;
     const int tok1 = min(L, tok0 + chunk_tokens);
     if (tok0 >= tok1) {                  // cannot happen with a consistent prefix; stay safe
-      if (lane == 0) next_item = workers + atomicAdd(p.work_counter, 1);
+      if (lane == 0) next_item = fixed_rounds ? next_item + workers : workers + atomicAdd(p.work_counter, 1);
       continue;
     }
 
@@ -495,7 +506,7 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     for (int it = 0; it < n_iter; ++it) {
       const int buf = it & 1;
       if (it == (n_iter > 1 ? n_iter - 2 : 0) && lane == 0)
-        next_item = workers + atomicAdd(p.work_counter, 1);
+        next_item = fixed_rounds ? next_item + workers : workers + atomicAdd(p.work_counter, 1);
       const uint32_t loaded = loaded_next;
       loaded_next = issue(it + 1, buf ^ 1);
       cp_async_wait<1>();

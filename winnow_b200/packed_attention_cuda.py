@@ -148,7 +148,45 @@ def packed_decode_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
     del allow_tf32, num_warps, num_stages
     if q.dim() == 4 and q.stride(-1) != 1:
         q = q.contiguous()
-    plan = DecodePlan(q, kv, scale, num_splits=num_splits, out=out, workspace=workspace,
-                      status=status, check_page_ids=check_page_ids)
+    key = _plan_key(q, kv, scale, num_splits, out, workspace, status)
+    plan = _PLANS.get(key) if key is not None and not check_page_ids else None
+    if plan is None:
+        plan = DecodePlan(q, kv, scale, num_splits=num_splits, out=out, workspace=workspace,
+                          status=status, check_page_ids=check_page_ids)
+        if key is not None and out is not None and workspace is not None:
+            if len(_PLANS) >= _PLAN_CACHE_SIZE:
+                _PLANS.pop(next(iter(_PLANS)))
+            _PLANS[key] = plan
+    if q.device.index == torch.cuda.current_device():
+        return plan.run()
     with torch.cuda.device(q.device):
         return plan.run()
+
+
+# Serving loops call the operator every step with the same buffers (query and
+# output staging tensors, one layer's pages, the batch's table and lengths,
+# updated in place).  When the caller supplies `out` and `workspace` and has
+# vouched for the page ids, the checked and marshalled call is remembered under
+# the identity (address, shape, strides) of every tensor involved, so a repeat
+# costs one dictionary lookup instead of the contract checks.  A plan keeps its
+# tensors alive, so a remembered address cannot be reused by another tensor.
+_PLANS: dict = {}
+_PLAN_CACHE_SIZE = 256
+
+
+def _ident(t: torch.Tensor):
+    return (t.data_ptr(), tuple(t.shape), t.stride(), t.dtype)
+
+
+def _plan_key(q, kv, scale, num_splits, out, workspace, status):
+    try:
+        return (_ident(q), _ident(kv.k_pages), _ident(kv.v_pages), _ident(kv.k_norms),
+                _ident(kv.v_norms), _ident(kv.page_table), _ident(kv.seq_lens),
+                kv.k_quant.Pi.data_ptr(), kv.k_quant.centroids.data_ptr(), kv.k_quant.bit_width,
+                kv.v_quant.Pi.data_ptr(), kv.v_quant.centroids.data_ptr(), kv.v_quant.bit_width,
+                kv.head_dim, float(scale), int(num_splits or 0),
+                None if out is None else _ident(out),
+                None if workspace is None else _ident(workspace),
+                None if status is None else status.data_ptr())
+    except Exception:                                  # noqa: BLE001 - malformed input: take the checked path
+        return None
