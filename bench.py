@@ -241,6 +241,18 @@ def run_ours(args):
     target = out_final if world == 1 else gathered[rank]
     plans = [DecodePlan(q_dev, kv, scale, num_splits=args.splits, check_page_ids=False,
                         out=target, workspace=ws) for kv in handles]
+    peer, exchange_note = None, "none"
+    if world > 1:
+        exchange_note = "nccl all_gather_into_tensor + permuting copy"
+        if args.exchange == "peer":
+            from winnow_b200 import tp
+            try:
+                peer = tp.PeerExchange(B, w.q_heads, D, w.dtype, dev)
+                plans[0].run_exchange(peer.descriptor(1), dry_run=True)
+                exchange_note = "fused: merge kernel stores to every rank's buffer over NVLink + flag wait"
+            except Exception as exc:                        # noqa: BLE001
+                peer = None
+                exchange_note += f" (peer exchange unavailable: {type(exc).__name__}: {exc})"
     graphs = [pl.graph() for pl in plans] if args.graph else None
 
     def gather():
@@ -251,6 +263,10 @@ def run_ours(args):
 
     def step(i):
         """Device-resident step: the pre-marshalled call (or its CUDA graph)."""
+        if peer is not None:
+            peer.step += 1
+            plans[i % layers].run_exchange(peer.descriptor(peer.step))
+            return peer.wait(peer.step)
         if graphs is not None:
             graphs[i % layers].replay()
         else:
@@ -259,6 +275,8 @@ def run_ours(args):
 
     def api_step(i):
         """The call a user makes, arguments checked and marshalled every time."""
+        if peer is not None:
+            return step(i)
         packed_decode_attention(q_dev, handles[i % layers], scale, num_splits=args.splits,
                                 check_page_ids=False, out=target, workspace=ws)
         return gather()
@@ -290,8 +308,11 @@ def run_ours(args):
         # second pass: same steps with events around the page-scan kernel only
         lib.wtq_profile_enable(args.steps + 8)
         for i in range(args.steps):
-            plans[(args.warmup + i) % layers].run()
-            gather()
+            if peer is not None:
+                step(args.warmup + i)
+            else:
+                plans[(args.warmup + i) % layers].run()
+                gather()
         torch.cuda.synchronize()
     import ctypes
     k_ms, k_n = ctypes.c_double(0.0), ctypes.c_int(0)
@@ -340,7 +361,7 @@ def run_ours(args):
                    "parallelism": f"kv-head tp{world}" if world > 1 else "single gpu",
                    "l2": f"steps rotate over {layers} layers of pages "
                          f"({layers * per_layer / 1e6:.0f} MB per GPU) so each step reads from HBM",
-                   "num_splits": args.splits or "auto",
+                   "num_splits": args.splits or "auto", "exchange": exchange_note,
                    "launch": "cuda graph replay" if args.graph else "pre-marshalled call"},
         "hbm_gbs": alg_total / (ms * 1e-3) / 1e9,
         "hbm_frac_of_8tbs_nominal": alg_total / (ms * 1e-3) / 1e9 / (NOMINAL_HBM_GBS * world),
@@ -456,6 +477,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--graph", action="store_true", help="replay each step as a CUDA graph")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="multi-GPU output exchange: fused peer stores, or NCCL all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -29,6 +29,15 @@ class Side(ctypes.Structure):
                 ("bw", c_int)]
 
 
+class Exchange(ctypes.Structure):
+    """Mirror of wtq_exchange_t (include/winnow_tq.h)."""
+    _fields_ = [("peer_out", c_void_p), ("peer_flags", c_void_p),
+                ("out_strides", c_int64 * 2), ("rank", c_int), ("world", c_int),
+                ("head_offset", c_int), ("step", ctypes.c_uint32), ("done_counter", c_void_p)]
+
+
+STATUS_EXCHANGE_TIMEOUT = 4
+
 _SIGNATURES = {
     "wtq_version": (c_int, []),
     "wtq_last_error": (ctypes.c_char_p, []),
@@ -52,6 +61,12 @@ _SIGNATURES = {
     "wtq_profile_collect": (c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_int)]),
     "wtq_profile_phases": (c_int, [ctypes.POINTER(ctypes.c_double)] * 3 + [ctypes.POINTER(c_int)]),
     "wtq_profile_disable": (c_int, []),
+    "wtq_decode_exchange": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64),
+                                    ctypes.POINTER(Exchange), ctypes.POINTER(Side),
+                                    ctypes.POINTER(Side), c_void_p, c_int64, c_void_p, c_float,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                    c_size_t, c_void_p, c_void_p]),
+    "wtq_exchange_wait": (c_int, [c_void_p, c_int, ctypes.c_uint32, c_int64, c_void_p, c_void_p]),
     "wtq_decode_static_capacity": (c_size_t, []),
     "wtq_decode_static": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p,
                                   ctypes.POINTER(c_int64), ctypes.POINTER(Side),

@@ -106,13 +106,13 @@ extern "C" size_t wtq_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int 
   return bytes;
 }
 
-extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], void *out,
-                          const int64_t out_strides[2], const wtq_side_t *k_side,
-                          const wtq_side_t *v_side, const int32_t *page_table,
-                          int64_t table_stride, const int32_t *seq_lens, float scale, int B,
-                          int Hq, int Hkv, int D, int S, int P, int max_pages, int num_splits,
-                          void *workspace, size_t workspace_bytes, int32_t *status,
-                          void *stream_) {
+static int decode_common(const void *q, int dtype, const int64_t q_strides[2], void *out,
+                         const int64_t out_strides[2], const wtq_exchange_t *exchange,
+                         const wtq_side_t *k_side, const wtq_side_t *v_side,
+                         const int32_t *page_table, int64_t table_stride, const int32_t *seq_lens,
+                         float scale, int B, int Hq, int Hkv, int D, int S, int P, int max_pages,
+                         int num_splits, void *workspace, size_t workspace_bytes, int32_t *status,
+                         void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (B < 0 || Hq < 1 || Hkv < 1 || S < 1 || P < 1 || max_pages < 1)
     return fail(WTQ_ERR_ARG, "wtq_decode: bad sizes");
@@ -128,7 +128,7 @@ extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], 
   DecodeParams p;
   if (!fill_side(p.k, *k_side, D) || !fill_side(p.v, *v_side, D))
     return fail(WTQ_ERR_ARG, "wtq_decode: null pages, norms, Pi or centroids");
-  if (!q || !out || !page_table || !seq_lens || !workspace)
+  if (!q || (!out && !exchange) || !page_table || !seq_lens || !workspace)
     return fail(WTQ_ERR_ARG, "wtq_decode: null input");
   const int splits = num_splits > 0 ? clamp_splits(num_splits, max_pages, S)
                                     : wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S,
@@ -161,7 +161,20 @@ extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], 
   m.part_acc = p.part_acc; m.part_m = p.part_m; m.part_l = p.part_l;
   m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
   m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
+  m.peer_out = nullptr; m.peer_flags = nullptr; m.done_counter = nullptr;
+  m.rank = m.world = m.head_offset = 0; m.step = 0;
+  if (exchange) {
+    if (exchange->world < 1 || exchange->rank < 0 || exchange->rank >= exchange->world ||
+        !exchange->peer_out || !exchange->peer_flags || !exchange->done_counter)
+      return fail(WTQ_ERR_ARG, "wtq_decode_exchange: malformed exchange descriptor");
+    m.peer_out = exchange->peer_out; m.peer_flags = exchange->peer_flags;
+    m.done_counter = exchange->done_counter; m.rank = exchange->rank; m.world = exchange->world;
+    m.head_offset = exchange->head_offset; m.step = exchange->step;
+  }
   const bool fast = mma_eligible(p) && !force_generic();
+  if (exchange && !fast)
+    return fail(WTQ_ERR_UNSUPPORTED, "wtq_decode_exchange: this shape runs on the generic kernels, "
+                "which have no exchange epilogue; gather with NCCL instead");
   // the tensor-core path works in the exp2 domain: fold log2(e) into the query
   const float q_scale = fast ? scale * 1.4426950408889634f : scale;
   const int max_tokens = max_pages * S;
@@ -180,4 +193,37 @@ extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], 
   }
   profile_mark_call(stream, false);
   return rc;
+}
+
+extern "C" int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], void *out,
+                          const int64_t out_strides[2], const wtq_side_t *k_side,
+                          const wtq_side_t *v_side, const int32_t *page_table,
+                          int64_t table_stride, const int32_t *seq_lens, float scale, int B,
+                          int Hq, int Hkv, int D, int S, int P, int max_pages, int num_splits,
+                          void *workspace, size_t workspace_bytes, int32_t *status,
+                          void *stream) {
+  if (!out || !out_strides) return fail(WTQ_ERR_ARG, "wtq_decode: null output");
+  return decode_common(q, dtype, q_strides, out, out_strides, nullptr, k_side, v_side, page_table,
+                       table_stride, seq_lens, scale, B, Hq, Hkv, D, S, P, max_pages, num_splits,
+                       workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int wtq_decode_exchange(const void *q, int dtype, const int64_t q_strides[2],
+                                   const wtq_exchange_t *exchange, const wtq_side_t *k_side,
+                                   const wtq_side_t *v_side, const int32_t *page_table,
+                                   int64_t table_stride, const int32_t *seq_lens, float scale,
+                                   int B, int Hq, int Hkv, int D, int S, int P, int max_pages,
+                                   int num_splits, void *workspace, size_t workspace_bytes,
+                                   int32_t *status, void *stream) {
+  if (!exchange) return fail(WTQ_ERR_ARG, "wtq_decode_exchange: null exchange descriptor");
+  return decode_common(q, dtype, q_strides, nullptr, exchange->out_strides, exchange, k_side,
+                       v_side, page_table, table_stride, seq_lens, scale, B, Hq, Hkv, D, S, P,
+                       max_pages, num_splits, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int wtq_exchange_wait(const uint32_t *local_flags, int world, uint32_t step,
+                                 int64_t spin_limit, int32_t *status, void *stream) {
+  if (!local_flags || world < 1 || world > 32 || spin_limit < 1)
+    return fail(WTQ_ERR_ARG, "wtq_exchange_wait: need flags, 1 <= world <= 32, spin_limit >= 1");
+  return launch_exchange_wait(local_flags, world, step, spin_limit, status, (cudaStream_t)stream);
 }

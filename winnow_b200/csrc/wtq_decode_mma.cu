@@ -795,13 +795,60 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
     for (int h = 0; h < 8; ++h) {
       if (h < hpb) {
         const float v = (o[h] + o_s[1][h][col]) + (o_s[2][h][col] + o_s[3][h][col]);
-        store_from_float(p.out, (int64_t)b * p.osb + (int64_t)(head0 + h) * p.osh + col, v,
-                         p.dtype);
+        if (p.world == 0) {
+          store_from_float(p.out, (int64_t)b * p.osb + (int64_t)(head0 + h) * p.osh + col, v,
+                           p.dtype);
+        } else {                          // the row goes to every rank's full buffer
+          const int64_t at = (int64_t)b * p.osb + (int64_t)(p.head_offset + head0 + h) * p.osh + col;
+          for (int r = 0; r < p.world; ++r) store_from_float(p.peer_out[r], at, v, p.dtype);
+        }
       }
     }
   }
   __syncthreads();                        // shared arrays are reused by the next group
   }
+  if (p.world > 0) {
+    // Publish: every block fences its peer stores and counts itself; the last
+    // one to arrive writes this rank's step into every rank's flag array.
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned blocks = gridDim.x * gridDim.y;
+      if (atomicAdd(p.done_counter, 1u) == blocks - 1) {
+        *p.done_counter = 0;
+        __threadfence_system();
+        for (int r = 0; r < p.world; ++r)
+          *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = p.step;
+        __threadfence_system();
+      }
+    }
+  }
+}
+
+// Waits (bounded) until every slot of the local flag array has reached `step`.
+__global__ void exchange_wait_kernel(const uint32_t *flags, int world, uint32_t step,
+                                     long long spin_limit, int32_t *status) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    const volatile uint32_t *slot = flags + r;
+    bool arrived = false;
+    for (long long i = 0; i < spin_limit; ++i) {
+      if ((int32_t)(*slot - step) >= 0) {
+        arrived = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (!arrived && status != nullptr) atomicOr(status, WTQ_STATUS_EXCHANGE_TIMEOUT);
+  }
+  __threadfence_system();
+}
+
+int launch_exchange_wait(const uint32_t *flags, int world, uint32_t step, long long spin_limit,
+                         int32_t *status, cudaStream_t stream) {
+  exchange_wait_kernel<<<1, 32, 0, stream>>>(flags, world, step, spin_limit, status);
+  note_launches(1);
+  return check_cuda(cudaGetLastError(), "wtq_exchange_wait launch");
 }
 
 // Worker warps per SM of the instantiation serving (bw_k, bw_v); 0 when the

@@ -115,6 +115,29 @@ class DecodePlan:
             _lib.check(rc)
         return self.out
 
+    def run_exchange(self, exchange, dry_run: bool = False):
+        """The call with its output exchange fused (`wtq_decode_exchange`):
+        `exchange` is a `_lib.Exchange` descriptor naming every rank's buffers.
+        `dry_run` only asks the library whether this shape has the fused
+        epilogue (raises `BackendError` if not) without launching anything."""
+        a = self._args
+        if dry_run:
+            probe = _lib.lib().wtq_decode_auto_splits(a[11], a[12], a[13], a[14], a[17], a[15],
+                                                      self._k_side.bw, self._v_side.bw)
+            eligible = (a[14] == 128 and (self._k_side.bw, self._v_side.bw) in
+                        ((4, 4), (4, 6), (6, 6), (8, 8)) and a[12] // a[13] <= 8
+                        and a[15] >= 16 and a[15] & (a[15] - 1) == 0 and probe >= 1)
+            if not eligible:
+                raise _lib.BackendError("no fused exchange epilogue for this shape")
+            return None
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        if not hasattr(self, "_fn_exchange"):
+            self._fn_exchange = _lib.lib().wtq_decode_exchange
+        rc = self._fn_exchange(a[0], a[1], a[2], ctypes.byref(exchange), *a[5:], stream)
+        if rc:
+            _lib.check(rc)
+        return None
+
     def graph(self) -> "torch.cuda.CUDAGraph":
         """The call captured as a CUDA graph (replay with `.replay()`)."""
         with torch.cuda.device(self.device):

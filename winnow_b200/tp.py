@@ -64,6 +64,83 @@ class HeadGather:
         return self.full
 
 
+class PeerExchange:
+    """Output exchange fused into the decode call: no collective library call.
+
+    Every rank allocates the same symmetric buffer (two full (B, Hq, 1, D)
+    outputs, used alternately, and a flag array) and maps its peers' copies.
+    The merge kernel of `wtq_decode_exchange` stores this rank's head rows into
+    every rank's buffer over NVLink and publishes the step number; a one-block
+    kernel (`wtq_exchange_wait`) then waits, with a bounded number of polls,
+    until all ranks have published.  Plain peer stores only, no multicast.
+    """
+
+    SPIN_LIMIT = 4_000_000            # polls of ~100 ns: gives up after a fraction of a second
+
+    def __init__(self, batch: int, q_heads: int, head_dim: int, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if q_heads % self.world:
+            raise ValueError(f"{q_heads} query heads do not shard over {self.world} ranks")
+        self.hq = q_heads // self.world
+        el = torch.empty((), dtype=dtype).element_size()
+        self.out_elems = batch * q_heads * head_dim
+        out_bytes = -(-self.out_elems * el // 256) * 256
+        total = 2 * out_bytes + 256
+        self._buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self._buf.zero_()
+        self._hdl = symm_mem.rendezvous(self._buf, self.group)
+        bases = [int(p) for p in self._hdl.buffer_ptrs]
+        dev = torch.device(device)
+        self._peer_out = [torch.tensor([b + i * out_bytes for b in bases], dtype=torch.int64, device=dev)
+                          for i in range(2)]
+        self._peer_flags = torch.tensor([b + 2 * out_bytes for b in bases], dtype=torch.int64, device=dev)
+        self.full = [self._buf[i * out_bytes: i * out_bytes + self.out_elems * el].view(dtype)
+                     .view(batch, q_heads, 1, head_dim) for i in range(2)]
+        self.flags = self._buf[2 * out_bytes: 2 * out_bytes + 4 * self.world].view(torch.int32)
+        self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.step = 0
+        self.device = dev
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)          # every rank's flags are zero before anyone publishes
+
+    def descriptor(self, step: int):
+        """The wtq_exchange_t of call number `step` (built once per buffer set;
+        only the step field changes from call to call)."""
+        from . import _lib
+        if not hasattr(self, "_desc"):
+            self._desc = []
+            for i in range(2):
+                ex = _lib.Exchange()
+                ex.peer_out = self._peer_out[i].data_ptr()
+                ex.peer_flags = self._peer_flags.data_ptr()
+                ex.out_strides[0], ex.out_strides[1] = self.full[i].stride(0), self.full[i].stride(1)
+                ex.rank, ex.world, ex.head_offset = self.rank, self.world, self.rank * self.hq
+                ex.done_counter = self.done.data_ptr()
+                self._desc.append(ex)
+            self._wait = _lib.lib().wtq_exchange_wait
+            self._wait_args = (self.flags.data_ptr(), self.world)
+            self._status_ptr = self.status.data_ptr()
+        ex = self._desc[step & 1]
+        ex.step = step
+        return ex
+
+    def wait(self, step: int) -> torch.Tensor:
+        rc = self._wait(*self._wait_args, step, self.SPIN_LIMIT, self._status_ptr,
+                        torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            from . import _lib
+            _lib.check(rc)
+        return self.full[step & 1]
+
+    def timed_out(self) -> bool:
+        """Host check of the status word (synchronises)."""
+        from . import _lib
+        return bool(int(self.status.item()) & _lib.STATUS_EXCHANGE_TIMEOUT)
+
+
 class TensorParallelDecode:
     """One rank's side of the sharded decode step.
 
@@ -74,15 +151,42 @@ class TensorParallelDecode:
     """
 
     def __init__(self, q_local: torch.Tensor, kv, scale: float, q_heads: int, *, group=None,
-                 num_splits: int | None = None, check_page_ids: bool = True):
+                 num_splits: int | None = None, check_page_ids: bool = True,
+                 exchange: str = "nccl"):
+        """`exchange="nccl"`: scan, then `all_gather_into_tensor` and a permuting
+        copy.  `exchange="peer"`: the merge kernel writes every rank's buffer
+        itself (`PeerExchange`); shapes without a tensor-core kernel fall back to
+        "nccl" (see `self.exchange`)."""
         from .packed_attention_cuda import DecodePlan
         B, hq, _, D = q_local.shape
-        self.heads = HeadGather(B, q_heads, D, q_local.dtype, q_local.device, group)
-        if hq != self.heads.hq:
-            raise ValueError(f"expected {self.heads.hq} local query heads, got {hq}")
-        self.plan = DecodePlan(q_local, kv, scale, num_splits=num_splits, out=self.heads.local,
-                               check_page_ids=check_page_ids)
+        self.exchange = exchange
+        self.peer = None
+        if exchange == "peer":
+            try:
+                self.peer = PeerExchange(B, q_heads, D, q_local.dtype, q_local.device, group)
+                if hq != self.peer.hq:
+                    raise ValueError(f"expected {self.peer.hq} local query heads, got {hq}")
+                self.plan = DecodePlan(q_local, kv, scale, num_splits=num_splits,
+                                       out=self.peer.full[0][:, :hq], check_page_ids=check_page_ids)
+                self.plan.run_exchange(self.peer.descriptor(1), dry_run=True)
+            except _lib_error() as exc:
+                self.peer, self.exchange = None, f"nccl (peer exchange unavailable: {exc})"
+        if self.peer is None:
+            self.heads = HeadGather(B, q_heads, D, q_local.dtype, q_local.device, group)
+            if hq != self.heads.hq:
+                raise ValueError(f"expected {self.heads.hq} local query heads, got {hq}")
+            self.plan = DecodePlan(q_local, kv, scale, num_splits=num_splits, out=self.heads.local,
+                                   check_page_ids=check_page_ids)
 
     def step(self) -> torch.Tensor:
-        self.plan.run()
-        return self.heads.gather()
+        if self.peer is None:
+            self.plan.run()
+            return self.heads.gather()
+        self.peer.step += 1
+        self.plan.run_exchange(self.peer.descriptor(self.peer.step))
+        return self.peer.wait(self.peer.step)
+
+
+def _lib_error():
+    from . import _lib
+    return (_lib.BackendError, RuntimeError, AttributeError, ImportError)
