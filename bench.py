@@ -248,12 +248,26 @@ def run_ours(args):
             from winnow_b200 import tp
             try:
                 peer = tp.PeerExchange(B, w.q_heads, D, w.dtype, dev)
-                plans[0].run_exchange(peer.descriptor(1), dry_run=True)
+                plans[0].run_exchange(peer.descriptor(), dry_run=True)
                 exchange_note = "fused: merge kernel stores to every rank's buffer over NVLink + flag wait"
             except Exception as exc:                        # noqa: BLE001
                 peer = None
                 exchange_note += f" (peer exchange unavailable: {type(exc).__name__}: {exc})"
-    graphs = [pl.graph() for pl in plans] if args.graph else None
+    graphs = None
+    if args.graph and peer is None:
+        graphs = [pl.graph() for pl in plans]
+    elif args.graph:
+        # one graph per layer: fused decode + bounded wait; every capture and its
+        # warm-up run is a real call of the exchange protocol on every rank
+        graphs = []
+        for pl in plans:
+            pl.run_exchange(peer.descriptor()); peer.wait(); peer.step += 1
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                pl.run_exchange(peer.descriptor()); peer.wait()
+            graphs.append(g)
+        barrier(world)
 
     def gather():
         if world > 1:
@@ -261,16 +275,24 @@ def run_ours(args):
             out_final.view(B, world, hq, 1, D).copy_(gathered.permute(1, 0, 2, 3, 4))
         return out_final
 
-    def step(i):
-        """Device-resident step: the pre-marshalled call (or its CUDA graph)."""
+    def direct_step(i):
+        """Device-resident step issued call by call (pre-marshalled arguments)."""
         if peer is not None:
             peer.step += 1
-            plans[i % layers].run_exchange(peer.descriptor(peer.step))
-            return peer.wait(peer.step)
-        if graphs is not None:
-            graphs[i % layers].replay()
-        else:
-            plans[i % layers].run()
+            plans[i % layers].run_exchange(peer.descriptor())
+            peer.wait()
+            return peer.result(peer.step)
+        plans[i % layers].run()
+        return gather()
+
+    def step(i):
+        """Device-resident step: the CUDA graph of `direct_step` when enabled."""
+        if graphs is None:
+            return direct_step(i)
+        graphs[i % layers].replay()
+        if peer is not None:
+            peer.step += 1
+            return peer.result(peer.step)
         return gather()
 
     def api_step(i):
@@ -308,11 +330,7 @@ def run_ours(args):
         # second pass: same steps with events around the page-scan kernel only
         lib.wtq_profile_enable(args.steps + 8)
         for i in range(args.steps):
-            if peer is not None:
-                step(args.warmup + i)
-            else:
-                plans[(args.warmup + i) % layers].run()
-                gather()
+            direct_step(args.warmup + i)
         torch.cuda.synchronize()
     import ctypes
     k_ms, k_n = ctypes.c_double(0.0), ctypes.c_int(0)
@@ -476,7 +494,8 @@ def main():
     ap.add_argument("--cpu-context", type=int, default=8192)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-check", action="store_true")
-    ap.add_argument("--graph", action="store_true", help="replay each step as a CUDA graph")
+    ap.add_argument("--graph", action=argparse.BooleanOptionalAction, default=True,
+                    help="replay each step as a CUDA graph (default) or issue the calls directly")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="multi-GPU output exchange: fused peer stores, or NCCL all-gather")
     args = ap.parse_args()

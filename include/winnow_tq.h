@@ -138,19 +138,22 @@ int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], void *out,
  * wtq_exchange_wait, enqueued after it, returns once all `world` slots of the
  * local flag array have reached `step`, i.e. the local full buffer is complete.
  * Waits are bounded: after `spin_limit` polls of a slot the kernel gives up,
- * sets WTQ_STATUS_EXCHANGE_TIMEOUT in `status` and returns.  `step` must grow
- * by one per call and the full buffers must alternate between two sets, because
- * a peer may already be writing step s+1 while this rank still reads step s.
+ * sets WTQ_STATUS_EXCHANGE_TIMEOUT in `status` and returns.  The step number
+ * lives in device memory (`step_counter`, zero at start, incremented by every
+ * call), so the call's arguments never change and it can be replayed from a
+ * CUDA graph; call number s (1, 2, ...) uses buffer set s & 1: the full buffers
+ * alternate between two sets because a peer may already be writing step s+1
+ * while this rank still reads step s.
  * Only the tensor-core path (head_dim 128, widths 4/4, 4/6, 6/6, 8/8) has this
  * epilogue; other shapes get WTQ_ERR_UNSUPPORTED and should gather with NCCL. */
 #define WTQ_STATUS_EXCHANGE_TIMEOUT 4
 typedef struct {
-  void *const *peer_out;          /* DEVICE array [world]: every rank's full output buffer */
+  void *const *peer_out[2];       /* DEVICE arrays [world]: every rank's full buffer, sets 0 and 1 */
   uint32_t *const *peer_flags;    /* DEVICE array [world]: every rank's flag array (world uint32) */
   int64_t out_strides[2];         /* element strides {batch, head} of the full buffers */
   int rank, world;
   int head_offset;                /* first head of the full buffer this rank writes */
-  uint32_t step;                  /* 1, 2, 3, ... */
+  uint32_t *step_counter;         /* local device uint32: calls completed so far */
   uint32_t *done_counter;         /* local device uint32, zero between calls */
 } wtq_exchange_t;
 int wtq_decode_exchange(const void *q, int dtype, const int64_t q_strides[2],
@@ -159,8 +162,8 @@ int wtq_decode_exchange(const void *q, int dtype, const int64_t q_strides[2],
                         const int32_t *seq_lens, float scale, int B, int Hq, int Hkv, int D, int S,
                         int P, int max_pages, int num_splits, void *workspace,
                         size_t workspace_bytes, int32_t *status, void *stream);
-int wtq_exchange_wait(const uint32_t *local_flags, int world, uint32_t step, int64_t spin_limit,
-                      int32_t *status, void *stream);
+int wtq_exchange_wait(const uint32_t *local_flags, int world, const uint32_t *step_counter,
+                      int64_t spin_limit, int32_t *status, void *stream);
 
 /* wtq_decode without a caller-supplied workspace.  It has no counterpart in the
  * reference.  It exists for hosts that cannot allocate device memory for this

@@ -31,9 +31,9 @@ class Side(ctypes.Structure):
 
 class Exchange(ctypes.Structure):
     """Mirror of wtq_exchange_t (include/winnow_tq.h)."""
-    _fields_ = [("peer_out", c_void_p), ("peer_flags", c_void_p),
+    _fields_ = [("peer_out", c_void_p * 2), ("peer_flags", c_void_p),
                 ("out_strides", c_int64 * 2), ("rank", c_int), ("world", c_int),
-                ("head_offset", c_int), ("step", ctypes.c_uint32), ("done_counter", c_void_p)]
+                ("head_offset", c_int), ("step_counter", c_void_p), ("done_counter", c_void_p)]
 
 
 STATUS_EXCHANGE_TIMEOUT = 4
@@ -66,7 +66,7 @@ _SIGNATURES = {
                                     ctypes.POINTER(Side), c_void_p, c_int64, c_void_p, c_float,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                     c_size_t, c_void_p, c_void_p]),
-    "wtq_exchange_wait": (c_int, [c_void_p, c_int, ctypes.c_uint32, c_int64, c_void_p, c_void_p]),
+    "wtq_exchange_wait": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "wtq_decode_static_capacity": (c_size_t, []),
     "wtq_decode_static": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p,
                                   ctypes.POINTER(c_int64), ctypes.POINTER(Side),

@@ -161,15 +161,18 @@ static int decode_common(const void *q, int dtype, const int64_t q_strides[2], v
   m.part_acc = p.part_acc; m.part_m = p.part_m; m.part_l = p.part_l;
   m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
   m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
-  m.peer_out = nullptr; m.peer_flags = nullptr; m.done_counter = nullptr;
-  m.rank = m.world = m.head_offset = 0; m.step = 0;
+  m.peer_out[0] = m.peer_out[1] = nullptr; m.peer_flags = nullptr;
+  m.done_counter = m.step_counter = nullptr;
+  m.rank = m.world = m.head_offset = 0;
   if (exchange) {
     if (exchange->world < 1 || exchange->rank < 0 || exchange->rank >= exchange->world ||
-        !exchange->peer_out || !exchange->peer_flags || !exchange->done_counter)
+        !exchange->peer_out[0] || !exchange->peer_out[1] || !exchange->peer_flags ||
+        !exchange->done_counter || !exchange->step_counter)
       return fail(WTQ_ERR_ARG, "wtq_decode_exchange: malformed exchange descriptor");
-    m.peer_out = exchange->peer_out; m.peer_flags = exchange->peer_flags;
-    m.done_counter = exchange->done_counter; m.rank = exchange->rank; m.world = exchange->world;
-    m.head_offset = exchange->head_offset; m.step = exchange->step;
+    m.peer_out[0] = exchange->peer_out[0]; m.peer_out[1] = exchange->peer_out[1];
+    m.peer_flags = exchange->peer_flags; m.done_counter = exchange->done_counter;
+    m.step_counter = exchange->step_counter; m.rank = exchange->rank; m.world = exchange->world;
+    m.head_offset = exchange->head_offset;
   }
   const bool fast = mma_eligible(p) && !force_generic();
   if (exchange && !fast)
@@ -221,9 +224,11 @@ extern "C" int wtq_decode_exchange(const void *q, int dtype, const int64_t q_str
                        max_pages, num_splits, workspace, workspace_bytes, status, stream);
 }
 
-extern "C" int wtq_exchange_wait(const uint32_t *local_flags, int world, uint32_t step,
-                                 int64_t spin_limit, int32_t *status, void *stream) {
-  if (!local_flags || world < 1 || world > 32 || spin_limit < 1)
+extern "C" int wtq_exchange_wait(const uint32_t *local_flags, int world,
+                                 const uint32_t *step_counter, int64_t spin_limit,
+                                 int32_t *status, void *stream) {
+  if (!local_flags || !step_counter || world < 1 || world > 32 || spin_limit < 1)
     return fail(WTQ_ERR_ARG, "wtq_exchange_wait: need flags, 1 <= world <= 32, spin_limit >= 1");
-  return launch_exchange_wait(local_flags, world, step, spin_limit, status, (cudaStream_t)stream);
+  return launch_exchange_wait(local_flags, world, step_counter, spin_limit, status,
+                              (cudaStream_t)stream);
 }

@@ -43,11 +43,10 @@ struct MergeParams {
   int dtype, Hq, D, num_splits;
   int32_t *work_counter;   // reset to zero by the merge (null on the generic path)
   // output exchange of KV-head tensor parallelism (world == 0: plain local store)
-  void *const *peer_out;
+  void *const *peer_out[2];
   uint32_t *const *peer_flags;
-  uint32_t *done_counter;
+  uint32_t *done_counter, *step_counter;
   int rank, world, head_offset;
-  uint32_t step;
 };
 
 // `chunk_prefix` (may be null): the launch also writes the exclusive prefix of
@@ -65,7 +64,8 @@ int mma_warps_per_sm(int bw_k, int bw_v);
 bool mma_eligible(const DecodeParams &p);
 int mma_chunk_tokens(int max_tokens, int splits);
 int launch_decode_mma(const DecodeParams &p, const MergeParams &m, cudaStream_t stream);
-int launch_exchange_wait(const uint32_t *flags, int world, uint32_t step, long long spin_limit,
+int launch_exchange_wait(const uint32_t *flags, int world, const uint32_t *step_counter,
+                         long long spin_limit,
                          int32_t *status, cudaStream_t stream);
 
 }  // namespace wtq

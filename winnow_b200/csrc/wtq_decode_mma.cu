@@ -681,6 +681,9 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
     }
   };
   if ((int)blockIdx.x < num_groups) preload(blockIdx.x);
+  // number of this call in the exchange protocol (the counter is advanced by
+  // the last block, after every block has read it: see the end of the kernel)
+  const uint32_t exchange_step = p.world > 0 ? *p.step_counter + 1u : 0u;
   for (int group = blockIdx.x; group < num_groups; group += gridDim.x) {
   const int b = group / Hkv, kvh = group - b * Hkv;
   const int head0 = kvh * n_rep + blockIdx.y * hpb;          // first query head of this pass
@@ -800,7 +803,8 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
                            p.dtype);
         } else {                          // the row goes to every rank's full buffer
           const int64_t at = (int64_t)b * p.osb + (int64_t)(p.head_offset + head0 + h) * p.osh + col;
-          for (int r = 0; r < p.world; ++r) store_from_float(p.peer_out[r], at, v, p.dtype);
+          void *const *dests = p.peer_out[exchange_step & 1u];
+          for (int r = 0; r < p.world; ++r) store_from_float(dests[r], at, v, p.dtype);
         }
       }
     }
@@ -810,15 +814,18 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
   if (p.world > 0) {
     // Publish: every block fences its peer stores and counts itself; the last
     // one to arrive writes this rank's step into every rank's flag array.
-    __threadfence_system();
+    // (the barrier makes the block's stores visible to thread 0, whose fence
+    // then orders them, cumulatively, before its arrival on the counter)
     __syncthreads();
     if (tid == 0) {
+      __threadfence_system();
       const unsigned blocks = gridDim.x * gridDim.y;
       if (atomicAdd(p.done_counter, 1u) == blocks - 1) {
         *p.done_counter = 0;
+        *p.step_counter = exchange_step;
         __threadfence_system();
         for (int r = 0; r < p.world; ++r)
-          *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = p.step;
+          *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = exchange_step;
         __threadfence_system();
       }
     }
@@ -826,9 +833,10 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
 }
 
 // Waits (bounded) until every slot of the local flag array has reached `step`.
-__global__ void exchange_wait_kernel(const uint32_t *flags, int world, uint32_t step,
+__global__ void exchange_wait_kernel(const uint32_t *flags, int world, const uint32_t *step_counter,
                                      long long spin_limit, int32_t *status) {
   const int r = threadIdx.x;
+  const uint32_t step = *step_counter;     // advanced by the merge kernel ahead of this one
   if (r < world) {
     const volatile uint32_t *slot = flags + r;
     bool arrived = false;
@@ -844,9 +852,9 @@ __global__ void exchange_wait_kernel(const uint32_t *flags, int world, uint32_t 
   __threadfence_system();
 }
 
-int launch_exchange_wait(const uint32_t *flags, int world, uint32_t step, long long spin_limit,
-                         int32_t *status, cudaStream_t stream) {
-  exchange_wait_kernel<<<1, 32, 0, stream>>>(flags, world, step, spin_limit, status);
+int launch_exchange_wait(const uint32_t *flags, int world, const uint32_t *step_counter,
+                         long long spin_limit, int32_t *status, cudaStream_t stream) {
+  exchange_wait_kernel<<<1, 32, 0, stream>>>(flags, world, step_counter, spin_limit, status);
   note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_exchange_wait launch");
 }

@@ -100,40 +100,43 @@ class PeerExchange:
                      .view(batch, q_heads, 1, head_dim) for i in range(2)]
         self.flags = self._buf[2 * out_bytes: 2 * out_bytes + 4 * self.world].view(torch.int32)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.step_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.step = 0
         self.device = dev
         torch.cuda.synchronize(dev)
         dist.barrier(self.group)          # every rank's flags are zero before anyone publishes
 
-    def descriptor(self, step: int):
-        """The wtq_exchange_t of call number `step` (built once per buffer set;
-        only the step field changes from call to call)."""
+    def descriptor(self):
+        """The wtq_exchange_t of this rank (constant: the step number lives in
+        device memory and is advanced by the kernels)."""
         from . import _lib
         if not hasattr(self, "_desc"):
-            self._desc = []
-            for i in range(2):
-                ex = _lib.Exchange()
-                ex.peer_out = self._peer_out[i].data_ptr()
-                ex.peer_flags = self._peer_flags.data_ptr()
-                ex.out_strides[0], ex.out_strides[1] = self.full[i].stride(0), self.full[i].stride(1)
-                ex.rank, ex.world, ex.head_offset = self.rank, self.world, self.rank * self.hq
-                ex.done_counter = self.done.data_ptr()
-                self._desc.append(ex)
+            ex = _lib.Exchange()
+            ex.peer_out[0] = self._peer_out[0].data_ptr()
+            ex.peer_out[1] = self._peer_out[1].data_ptr()
+            ex.peer_flags = self._peer_flags.data_ptr()
+            ex.out_strides[0], ex.out_strides[1] = self.full[0].stride(0), self.full[0].stride(1)
+            ex.rank, ex.world, ex.head_offset = self.rank, self.world, self.rank * self.hq
+            ex.step_counter = self.step_dev.data_ptr()
+            ex.done_counter = self.done.data_ptr()
+            self._desc = ex
             self._wait = _lib.lib().wtq_exchange_wait
-            self._wait_args = (self.flags.data_ptr(), self.world)
-            self._status_ptr = self.status.data_ptr()
-        ex = self._desc[step & 1]
-        ex.step = step
-        return ex
+            self._wait_args = (self.flags.data_ptr(), self.world, self.step_dev.data_ptr(),
+                               self.SPIN_LIMIT, self.status.data_ptr())
+        return self._desc
 
-    def wait(self, step: int) -> torch.Tensor:
-        rc = self._wait(*self._wait_args, step, self.SPIN_LIMIT, self._status_ptr,
-                        torch.cuda.current_stream(self.device).cuda_stream)
+    def wait(self) -> None:
+        """Enqueue the bounded wait for every rank's rows of the latest call."""
+        rc = self._wait(*self._wait_args, torch.cuda.current_stream(self.device).cuda_stream)
         if rc:
             from . import _lib
             _lib.check(rc)
-        return self.full[step & 1]
+
+    def result(self, call_number: int) -> torch.Tensor:
+        """Full output of call number `call_number` (1, 2, ...), valid once the
+        wait enqueued after that call has run."""
+        return self.full[call_number & 1]
 
     def timed_out(self) -> bool:
         """Host check of the status word (synchronises)."""
@@ -168,7 +171,7 @@ class TensorParallelDecode:
                     raise ValueError(f"expected {self.peer.hq} local query heads, got {hq}")
                 self.plan = DecodePlan(q_local, kv, scale, num_splits=num_splits,
                                        out=self.peer.full[0][:, :hq], check_page_ids=check_page_ids)
-                self.plan.run_exchange(self.peer.descriptor(1), dry_run=True)
+                self.plan.run_exchange(self.peer.descriptor(), dry_run=True)
             except _lib_error() as exc:
                 self.peer, self.exchange = None, f"nccl (peer exchange unavailable: {exc})"
         if self.peer is None:
@@ -183,8 +186,9 @@ class TensorParallelDecode:
             self.plan.run()
             return self.heads.gather()
         self.peer.step += 1
-        self.plan.run_exchange(self.peer.descriptor(self.peer.step))
-        return self.peer.wait(self.peer.step)
+        self.plan.run_exchange(self.peer.descriptor())
+        self.peer.wait()
+        return self.peer.result(self.peer.step)
 
 
 def _lib_error():
