@@ -412,7 +412,6 @@ def time_append(w, pool, handles, rank, world, dev, args):
     tokens overwrite the last stored position of every sequence with the vector
     already there, so the cache the decode step reads is unchanged."""
     from winnow_b200.cache import _get_quantizer
-    from winnow_b200.packed_backend import append_tokens
     hkv = w.kv_heads // world
     kq = _get_quantizer(w.bits_k, w.head_dim, dev, 42)
     vq = _get_quantizer(w.bits_v, w.head_dim, dev, 43)
@@ -421,16 +420,19 @@ def time_append(w, pool, handles, rank, world, dev, args):
     v = v[:, rank * hkv:(rank + 1) * hkv].to(dev)
     spare = pool.k_pages.shape[0] - 1                          # scratch layer: the last one
     kv = handles[spare]
+    from winnow_b200.packed_backend import AppendPlan
+    plan = AppendPlan(k, v, kv.k_pages, kv.k_norms, kv.v_pages, kv.v_norms, kv.page_table,
+                      kv.seq_lens, kq, vq)
     times = []
-    for i in range(5 + 20):
+    for i in range(3 + 7):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        append_tokens(k, v, kv.k_pages, kv.k_norms, kv.v_pages, kv.v_norms, kv.page_table,
-                      kv.seq_lens, kq, vq)
+        for _ in range(20):                                    # back to back: device time per append
+            plan.run()
         e.record()
         torch.cuda.synchronize()
-        if i >= 5:
-            times.append(s.elapsed_time(e) * 1e3)
+        if i >= 3:
+            times.append(s.elapsed_time(e) * 1e3 / 20)
     return statistics.median(times)
 
 

@@ -25,6 +25,7 @@ struct QuantSideDev {
   const float *Pi;
   const float *bounds;
   int bw, nb, nbounds;
+  bool vec4;      // Pi is 16-byte aligned and D a multiple of 4: rows can be read as float4
 };
 
 struct QuantScratch {
@@ -63,7 +64,54 @@ __device__ void quantize_vector(QuantScratch &s, const float *pi_s, const QuantS
   __syncthreads();
   if (c < D) {
     float y;
-    if (order == WTQ_ORDER_INTERLEAVED16) {
+    if (!STAGE && q.vec4) {
+      // Few vectors per block: staging all of Pi would cost more than it saves.
+      // The thread walks its own row of Pi with 16-byte loads, eight in flight;
+      // the summation order is the same as below.
+      const float4 *row = reinterpret_cast<const float4 *>(q.Pi + (int64_t)c * D);
+      if (order == WTQ_ORDER_INTERLEAVED16) {
+        float ch[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) ch[j] = 0.0f;
+        for (int d0 = 0; d0 < D; d0 += 16) {
+          float4 w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) w[j] = d0 + 4 * j < D ? __ldg(row + d0 / 4 + j) : make_float4(0, 0, 0, 0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (d0 + 4 * j < D) {
+              ch[4 * j + 0] = __fmaf_rn(s.x[d0 + 4 * j + 0], w[j].x, ch[4 * j + 0]);
+              ch[4 * j + 1] = __fmaf_rn(s.x[d0 + 4 * j + 1], w[j].y, ch[4 * j + 1]);
+              ch[4 * j + 2] = __fmaf_rn(s.x[d0 + 4 * j + 2], w[j].z, ch[4 * j + 2]);
+              ch[4 * j + 3] = __fmaf_rn(s.x[d0 + 4 * j + 3], w[j].w, ch[4 * j + 3]);
+            }
+          }
+        }
+        float part[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          part[j] = __fadd_rn(__fadd_rn(__fadd_rn(ch[j], ch[j + 4]), ch[j + 8]), ch[j + 12]);
+        y = __fadd_rn(__fadd_rn(part[0], part[1]), __fadd_rn(part[2], part[3]));
+      } else {
+        float acc = 0.0f;
+        for (int j0 = 0; j0 < D / 4; j0 += 8) {
+          float4 w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w[j] = j0 + j < D / 4 ? __ldg(row + j0 + j) : make_float4(0, 0, 0, 0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (j0 + j < D / 4) {
+              const int d = 4 * (j0 + j);
+              acc = __fmaf_rn(s.x[d + 0], w[j].x, acc);
+              acc = __fmaf_rn(s.x[d + 1], w[j].y, acc);
+              acc = __fmaf_rn(s.x[d + 2], w[j].z, acc);
+              acc = __fmaf_rn(s.x[d + 3], w[j].w, acc);
+            }
+          }
+        }
+        y = acc;
+      }
+    } else if (order == WTQ_ORDER_INTERLEAVED16) {
       float ch[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) ch[j] = 0.0f;
@@ -222,15 +270,19 @@ static int launch_staged(K staged, K direct, P &params, int D, int64_t work, int
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const bool stage = D <= 128;
+  // Staging Pi in shared memory (64 KB per block at head_dim 128) pays off when
+  // a block quantizes many vectors (bulk fills); a decode step appends a few
+  // hundred vectors in all, so there every vector gets its own block and the
+  // threads read their rows of Pi directly.
+  int64_t blocks = work < (int64_t)sms * 3 ? work : (int64_t)sms * 3;
+  if (blocks < 1) blocks = 1;
+  const bool stage = D <= 128 && work > 4 * blocks;
   const size_t smem = stage ? (size_t)D * (D + 1) * sizeof(float) : 0;
   if (stage && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(staged, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return check_cuda(e, what);
   }
-  int64_t blocks = work < (int64_t)sms * 3 ? work : (int64_t)sms * 3;
-  if (blocks < 1) blocks = 1;
   dim3 grid((unsigned)blocks, (unsigned)sides);
   if (stage) staged<<<grid, block_threads(D), smem, stream>>>(params);
   else direct<<<grid, block_threads(D), 0, stream>>>(params);
@@ -254,7 +306,7 @@ extern "C" int wtq_quantize(const void *x, int dtype, int64_t rows, int64_t row_
   QuantizeParams p;
   p.x = x; p.dtype = dtype; p.rows = rows; p.row_stride = row_stride; p.D = D;
   p.order = resolve_order(order, rows);
-  p.side = {Pi, bounds, bw, D * bw / 8, (1 << bw) - 1};
+  p.side = {Pi, bounds, bw, D * bw / 8, (1 << bw) - 1, D % 4 == 0 && ((uintptr_t)Pi & 15) == 0};
   p.idx = idx; p.packed = packed; p.norms = norms;
   return launch_staged(quantize_kernel<true>, quantize_kernel<false>, p, D, rows, 1,
                        (cudaStream_t)stream, "wtq_quantize launch");
@@ -283,7 +335,8 @@ extern "C" int wtq_append(const void *k, const void *v, int dtype, const int64_t
     if (!w.pages || !w.norms || !w.Pi || !w.bounds)
       return fail(WTQ_ERR_ARG, "wtq_append: null pages, norms, Pi or bounds");
     AppendSideDev &a = p.side[s];
-    a.q = {w.Pi, w.bounds, w.bw, D * w.bw / 8, (1 << w.bw) - 1};
+    a.q = {w.Pi, w.bounds, w.bw, D * w.bw / 8, (1 << w.bw) - 1,
+           D % 4 == 0 && ((uintptr_t)w.Pi & 15) == 0};
     a.src = src[s];
     a.sb = strides[s][0]; a.sh = strides[s][1]; a.st = strides[s][2];
     a.pages = w.pages; a.norms = (__half *)w.norms;

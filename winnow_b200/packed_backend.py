@@ -171,6 +171,53 @@ class PagedPackedCache:
         return handle, handle
 
 
+class AppendPlan:
+    """One fused append (wtq_append) with every argument checked and marshalled
+    ahead of time; `run()` is a single library call on the current stream.  The
+    plan keeps its tensors alive and can be reused while they are updated in
+    place (new K/V written into the same staging tensors, lengths advanced)."""
+
+    def __init__(self, k, v, k_pages, k_norms, v_pages, v_norms, page_table, seq_lens, k_tq, v_tq,
+                 *, order: int = _lib.ORDER_AUTO, status: torch.Tensor | None = None):
+        dev = _lib.require_cuda(k, v, k_pages, v_pages, k_norms, v_norms, page_table, seq_lens)
+        B, Hkv, n, D = k.shape
+        if v.shape != k.shape or v.dtype != k.dtype:
+            raise ValueError("k and v must have the same shape and dtype")
+        if k.stride(-1) != 1 or v.stride(-1) != 1:
+            raise ValueError("k and v need unit stride in their last dimension")
+        P, Hp, S, _ = k_pages.shape
+        if Hp != Hkv or v_pages.shape[:3] != k_pages.shape[:3]:
+            raise ValueError("pages do not match (P, Hkv, S, NB)")
+        for pages, norms, tq in ((k_pages, k_norms, k_tq), (v_pages, v_norms, v_tq)):
+            if pages.shape[-1] != packed_bytes(D, tq.bit_width) or pages.stride(-1) != 1 \
+                    or pages.stride(-2) != pages.shape[-1] or norms.stride(-1) != 1 \
+                    or norms.dtype != torch.float16 or pages.dtype != torch.uint8:
+                raise ValueError("pages/norms layout does not match the quantizer")
+        if page_table.dtype != torch.int32 or seq_lens.dtype != torch.int32 \
+                or page_table.stride(-1) != 1 or not seq_lens.is_contiguous():
+            raise ValueError("page_table and seq_lens must be contiguous int32")
+        self.device = dev
+        self._keep = (k, v, k_pages, k_norms, v_pages, v_norms, page_table, seq_lens, k_tq, v_tq, status)
+        self._sides = [
+            _lib.Side(pages.data_ptr(), norms.data_ptr(), pages.stride(0), pages.stride(1),
+                      norms.stride(0), norms.stride(1), tq.Pi.data_ptr(), tq.boundaries.data_ptr(),
+                      tq.centroids.data_ptr(), tq.bit_width)
+            for pages, norms, tq in ((k_pages, k_norms, k_tq), (v_pages, v_norms, v_tq))]
+        self._ks = _lib.i64x(k.stride(0), k.stride(1), k.stride(2))
+        self._vs = _lib.i64x(v.stride(0), v.stride(1), v.stride(2))
+        self._fn = _lib.lib().wtq_append
+        self._args = (k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype), self._ks, self._vs,
+                      ctypes.byref(self._sides[0]), ctypes.byref(self._sides[1]),
+                      page_table.data_ptr(), page_table.stride(0), seq_lens.data_ptr(),
+                      B, Hkv, n, D, S, P, page_table.shape[1], order,
+                      status.data_ptr() if status is not None else None)
+
+    def run(self) -> None:
+        rc = self._fn(*self._args, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            _lib.check(rc)
+
+
 @torch.no_grad()
 def append_tokens(k, v, k_pages, k_norms, v_pages, v_norms, page_table, seq_lens, k_tq, v_tq, *,
                   order: int = _lib.ORDER_AUTO, status: torch.Tensor | None = None) -> None:
@@ -181,39 +228,14 @@ def append_tokens(k, v, k_pages, k_norms, v_pages, v_norms, page_table, seq_lens
     `seq_lens` already includes the n new tokens, so token i of sequence b is
     written at position seq_lens[b] - n + i.
     """
-    dev = _lib.require_cuda(k, v, k_pages, v_pages, k_norms, v_norms, page_table, seq_lens)
-    B, Hkv, n, D = k.shape
-    if v.shape != k.shape or v.dtype != k.dtype:
-        raise ValueError("k and v must have the same shape and dtype")
     if k.stride(-1) != 1:
         k = k.contiguous()
     if v.stride(-1) != 1:
         v = v.contiguous()
-    P, Hp, S, _ = k_pages.shape
-    if Hp != Hkv or v_pages.shape[:3] != k_pages.shape[:3]:
-        raise ValueError("pages do not match (P, Hkv, S, NB)")
-    for pages, norms, tq in ((k_pages, k_norms, k_tq), (v_pages, v_norms, v_tq)):
-        if pages.shape[-1] != packed_bytes(D, tq.bit_width) or pages.stride(-1) != 1 \
-                or pages.stride(-2) != pages.shape[-1] or norms.stride(-1) != 1 \
-                or norms.dtype != torch.float16 or pages.dtype != torch.uint8:
-            raise ValueError("pages/norms layout does not match the quantizer")
-    if page_table.dtype != torch.int32 or seq_lens.dtype != torch.int32 \
-            or page_table.stride(-1) != 1 or not seq_lens.is_contiguous():
-        raise ValueError("page_table and seq_lens must be contiguous int32")
-    sides = []
-    for pages, norms, tq in ((k_pages, k_norms, k_tq), (v_pages, v_norms, v_tq)):
-        sides.append(_lib.Side(pages.data_ptr(), norms.data_ptr(), pages.stride(0), pages.stride(1),
-                               norms.stride(0), norms.stride(1), tq.Pi.data_ptr(),
-                               tq.boundaries.data_ptr(), tq.centroids.data_ptr(), tq.bit_width))
-    with torch.cuda.device(dev):
-        _lib.check(_lib.lib().wtq_append(
-            k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype),
-            _lib.i64x(k.stride(0), k.stride(1), k.stride(2)),
-            _lib.i64x(v.stride(0), v.stride(1), v.stride(2)),
-            ctypes.byref(sides[0]), ctypes.byref(sides[1]),
-            page_table.data_ptr(), page_table.stride(0), seq_lens.data_ptr(),
-            B, Hkv, n, D, S, P, page_table.shape[1], order,
-            status.data_ptr() if status is not None else None, _lib.stream_ptr(dev)))
+    plan = AppendPlan(k, v, k_pages, k_norms, v_pages, v_norms, page_table, seq_lens, k_tq, v_tq,
+                      order=order, status=status)
+    with torch.cuda.device(plan.device):
+        plan.run()
 
 
 def select_decode_backend(query: torch.Tensor, kv, requested: str) -> str:
