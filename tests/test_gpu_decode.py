@@ -257,3 +257,32 @@ def test_repeated_calls_reuse_the_marshalled_plan():
     # a checked call never uses the cache
     packed_decode_attention(qd, kv, scale, out=out, workspace=ws)
     assert len(pac._PLANS) == 1
+
+
+def test_legacy_contiguous_cache_roundtrip():
+    """TQPackedLayer: write in place, dequantize the history; against the oracle."""
+    from winnow_b200.cache import TQPackedCache
+    g = torch.Generator().manual_seed(12)
+    B, H, D, bw = 2, 3, 128, 4
+    cache = TQPackedCache(D, bw, DEV, max_cache_len=64, num_layers=2)
+    o = orc.OracleQuantizer.get(bw, D, 42)
+    hist_k, hist_v = [], []
+    for n in (17, 1, 1):                               # a prefill chunk, then two decode steps
+        k = torch.randn(B, H, n, D, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, H, n, D, generator=g).to(torch.bfloat16)
+        hist_k.append(k), hist_v.append(v)
+        K, V = cache.update(k.to(DEV), v.to(DEV), 1)
+    assert cache.get_seq_length(1) == 19 and K.shape == (B, H, 19, D) and K.dtype == torch.bfloat16
+    for dense, got in ((torch.cat(hist_k, 2), K), (torch.cat(hist_v, 2), V)):
+        # same call grouping as the cache's three updates
+        parts = []
+        for chunk in dense.split([17, 1, 1], dim=2):
+            idx, nrm = o.quantize(chunk)
+            parts.append(orc.dequantize_rows(orc.pack(idx, bw), nrm.to(torch.float16),
+                                             o.centroids, o.Pi, bw, D))
+        ref = torch.cat(parts, 2).to(torch.bfloat16).float()
+        ulp = (ref.abs() * 2.0 ** -7).clamp(min=1e-30)
+        assert ((got.float().cpu() - ref).abs() <= ulp).all()
+    assert cache.layers[1].last_dispatch_decision.backend == "cuda_sm100"
+    with pytest.raises(RuntimeError):
+        cache.update(torch.zeros(B, H, 64, D, device=DEV), torch.zeros(B, H, 64, D, device=DEV), 1)

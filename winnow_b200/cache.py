@@ -165,3 +165,95 @@ def _get_quantizer(bw, dim, dev, seed=42) -> TurboQuantMSE:
     if key not in _QUANTIZER_CACHE:
         _QUANTIZER_CACHE[key] = TurboQuantMSE(bw, dim, dev, rotation_seed=seed)
     return _QUANTIZER_CACHE[key]
+
+
+class TQPackedLayer:
+    """Contiguous packed KV of one layer: a preallocated (B, H, max_len, NB) ring
+    of codes plus fp16 norms, written in place, and a transient dequantization
+    of the whole history per step (reference: turboquant_kv/cache.py:154-330).
+
+    This is the legacy cache of the reference: it hands dense K, V to stock
+    attention, so its decode cost grows with the history.  The paged cache with
+    compressed-domain attention (packed_backend.PagedPackedCache) is the path
+    to use; this class exists for callers that still hold the old interface.
+    Both directions run on the GPU: `wtq_quantize` with fused packing for the
+    write, `wtq_dequant` reading the ring in place for the read.  The outlier
+    channel variant of the reference (two quantizers over a channel mask) is
+    not provided.
+    """
+
+    def __init__(self, head_dim: int, bit_width: int, device, max_cache_len: int,
+                 num_outlier_channels: int = 0, outlier_bits: int = 0, **_ignored):
+        if num_outlier_channels > 0 and outlier_bits > bit_width:
+            raise NotImplementedError("outlier channels are not supported by the CUDA backend")
+        self._bw, self._hd, self._max = bit_width, head_dim, max_cache_len
+        self._tq = _get_quantizer(bit_width, head_dim, device)
+        self._nb = packed_bytes(head_dim, bit_width)
+        self._len = 0
+        self.is_initialized = False
+        self.last_dispatch_decision = None
+
+    def lazy_initialization(self, ks: torch.Tensor, vs: torch.Tensor) -> None:
+        from .dispatch import Hardware, NumericalContract, Shape, default_dispatcher
+        B, H, _, D = ks.shape
+        dev = _lib.require_cuda(ks, vs)
+        self.dtype, self.device = ks.dtype, dev
+        self._pk = torch.empty(B, H, self._max, self._nb, dtype=torch.uint8, device=dev)
+        self._pv = torch.empty_like(self._pk)
+        self._nk = torch.empty(B, H, self._max, dtype=torch.float16, device=dev)
+        self._nv = torch.empty_like(self._nk)
+        self._shape = (B, H, D)
+        self.last_dispatch_decision = default_dispatcher().select(
+            Hardware.from_torch(torch, dev), Shape(B, H, self._max, D, self._bw),
+            NumericalContract.quantization_aware())
+        if self.last_dispatch_decision.backend == "none":
+            raise _lib.BackendError(self.last_dispatch_decision.reason)
+        self.is_initialized = True
+
+    def _store(self, x, pos, n, codes, norms):
+        packed, nrm = self._tq.quantize(x, packed=True)
+        codes[:, :, pos:pos + n] = packed
+        norms[:, :, pos:pos + n] = nrm.to(torch.float16)
+
+    def _load(self, length, codes, norms):
+        B, H, D = self._shape
+        out = torch.empty(B, H, length, D, dtype=self.dtype, device=self.device)
+        return dequantize_rows(codes[:, :, :length], norms[:, :, :length], self._tq.centroids,
+                               self._tq.Pi, self._bw, D, out=out)
+
+    def get_seq_length(self) -> int:
+        return self._len
+
+    @torch.no_grad()
+    def update(self, key_states, value_states, *args, **kwargs):
+        if not self.is_initialized:
+            self.lazy_initialization(key_states, value_states)
+        n = key_states.shape[-2]
+        if self._len + n > self._max:
+            raise RuntimeError(f"TQPackedLayer overflow: {self._len}+{n} > max_cache_len="
+                               f"{self._max}. Raise max_cache_len.")
+        self._store(key_states, self._len, n, self._pk, self._nk)
+        self._store(value_states, self._len, n, self._pv, self._nv)
+        self._len += n
+        return self._load(self._len, self._pk, self._nk), self._load(self._len, self._pv, self._nv)
+
+    def packed_bytes_held(self) -> int:
+        """Persistent bytes of this layer (codes + norms for the whole ring)."""
+        if not self.is_initialized:
+            return 0
+        return sum(t.numel() * t.element_size() for t in (self._pk, self._pv, self._nk, self._nv))
+
+
+class TQPackedCache:
+    """A list of `TQPackedLayer`s with the `update(k, v, layer_idx)` protocol."""
+
+    def __init__(self, head_dim: int, bit_width: int, device, max_cache_len: int,
+                 num_layers: int, **layer_kwargs):
+        self.layers = [TQPackedLayer(head_dim, bit_width, device, max_cache_len, **layer_kwargs)
+                       for _ in range(num_layers)]
+
+    def update(self, key_states, value_states, layer_idx: int, *args, **kwargs):
+        return self.layers[layer_idx].update(key_states, value_states)
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return self.layers[layer_idx].get_seq_length()
