@@ -353,6 +353,7 @@ def run_ours(args):
     # ---- fused append of one token per sequence (reported beside the step)
     append_us = time_append(w, pool, handles, rank, world, dev, args)
 
+    exchange_ok = True if peer is None else not peer.timed_out()
     if rank != 0:
         return
     peak, peak_kind = measured_peak()
@@ -396,6 +397,7 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "clocks": clocks.summary(),
         "parity_max_abs_err_vs_oracle": parity,
+        "exchange_completed_without_timeout": exchange_ok,
     }
     print(json.dumps(line))
 
@@ -442,6 +444,9 @@ def run_reference(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
     from oracle import tq_oracle as orc
+    # torchrun pins OMP_NUM_THREADS=1 for its children; the CPU arm is entitled to
+    # every host core
+    torch.set_num_threads(os.cpu_count() or 1)
     w = workloads.WORKLOADS[args.workload]
     seqs = max(1, min(w.batch, args.cpu_seqs))
     kq = orc.OracleQuantizer.get(w.bits_k, w.head_dim, 42)

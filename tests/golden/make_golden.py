@@ -1,9 +1,9 @@
 """Regenerate the golden vectors under tests/golden/ from the reference itself.
 
-Run in a checkout that has the reference project mounted (default
-/root/reference, override with WINNOW_REFERENCE):
+Run where a checkout of the reference project is available and point
+WINNOW_REFERENCE at it:
 
-    python tests/golden/make_golden.py
+    WINNOW_REFERENCE=/path/to/winnow python tests/golden/make_golden.py
 
 It imports the reference's own modules (packing, cache, packed_attention,
 page_pool, packed_backend) read-only, runs them on the CPU on the seeded inputs
@@ -23,7 +23,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(os.environ.get("WINNOW_REFERENCE", "/root/reference")) / "turboquant_kv"
+REF = Path(os.environ.get("WINNOW_REFERENCE", "reference")) / "turboquant_kv"
 sys.dont_write_bytecode = True
 sys.path.insert(0, str(REF))
 sys.path.insert(0, str(ROOT))
@@ -107,7 +107,7 @@ def attention_vectors():
 
 
 def config1_vectors():
-    """BASELINE config 1 end to end: pages bytes, norms, table and outputs."""
+    """Benchmark configuration 1 end to end: pages bytes, norms, table and outputs."""
     w = workloads.WORKLOADS["config1"]
     k, v = workloads.dense_kv(w, 0)
     q = workloads.queries(w)

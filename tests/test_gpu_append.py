@@ -117,7 +117,7 @@ def test_append_refuses_pages_outside_the_pool():
 
 
 def test_config1_cache_bit_exact(golden):
-    """BASELINE config 1: the whole packed cache built on the GPU equals the
+    """Benchmark configuration 1: the whole packed cache built on the GPU equals the
     reference's bytes."""
     g = golden("config1")
     w = workloads.WORKLOADS["config1"]

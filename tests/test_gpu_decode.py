@@ -286,3 +286,17 @@ def test_legacy_contiguous_cache_roundtrip():
     assert cache.layers[1].last_dispatch_decision.backend == "cuda_sm100"
     with pytest.raises(RuntimeError):
         cache.update(torch.zeros(B, H, 64, D, device=DEV), torch.zeros(B, H, 64, D, device=DEV), 1)
+
+
+def test_more_sequences_than_the_shared_prefix_holds():
+    """1100 short ragged sequences: the chunk prefix no longer fits the kernel's
+    shared-memory copy, so the work queue reads the one in the workspace."""
+    g = torch.Generator().manual_seed(77)
+    lens = tuple(int(x) for x in torch.randint(0, 41, (1100,), generator=g))
+    c = cases.AttnCase("many", 78, len(lens), 2, 1, 128, lens, 16, 4, 4)
+    q, okv, _ = oracle_case(c)
+    got = packed_decode_attention(q.to(DEV), to_device(okv, DEV), orc.default_scale(128))
+    assert_attention_close(got, orc.tiled_attention(q, okv, orc.default_scale(128)))
+    for b, L in enumerate(lens):
+        if L == 0:
+            assert (got[b] == 0).all()

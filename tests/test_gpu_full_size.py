@@ -1,4 +1,4 @@
-"""BASELINE-sized workloads, checked through properties that do not need a CPU
+"""Full-size benchmark workloads, checked through properties that do not need a CPU
 reference of the whole thing: the split count must not change the result, the
 tensor-core and generic kernels must agree, scaling the value norms scales the
 output, relabelling pages leaves it unchanged, and a slice small enough for the

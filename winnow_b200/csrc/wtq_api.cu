@@ -73,14 +73,25 @@ extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pag
     const int64_t workers = (int64_t)device_sms() * warps;
     int64_t chunk = (max_tokens * groups + 3 * workers - 1) / (3 * workers);
     chunk = (chunk + 63) / 64 * 64;
-    // work is handed out dynamically, so only the tail matters: a chunk above
-    // 512 tokens would leave one warp running long after the others are done
+    // a chunk above 512 tokens would leave one warp running long after the
+    // others are done; below 256 the partial states start to cost
     if (chunk < 256) chunk = 256;
     if (chunk > 512) chunk = 512;
+    // ... unless the whole step is so small (few kv heads per GPU, short
+    // batches) that 256-token chunks would not even give every warp one item:
+    // then the chunk shrinks, down to 64 tokens, until there are about two
+    // items per warp
+    const int64_t items = groups * ((max_tokens + chunk - 1) / chunk);
+    if (items < 2 * workers) {
+      int64_t small = (max_tokens * groups + 2 * workers - 1) / (2 * workers);
+      small = (small + 31) / 32 * 32;
+      if (small < 64) small = 64;
+      if (small < chunk) chunk = small;
+    }
     if (chunk * kMaxSplits < max_tokens) chunk = ((max_tokens + kMaxSplits - 1) / kMaxSplits + 63) / 64 * 64;
     int64_t splits = (max_tokens + chunk - 1) / chunk;
     if (splits > kMaxSplits) splits = kMaxSplits;
-    return clamp_splits((int)splits, max_pages, S);
+    return splits < 1 ? 1 : (int)splits;
   }
   // generic path: about eight 128-thread blocks per SM
   const int64_t want = (int64_t)device_sms() * 8;

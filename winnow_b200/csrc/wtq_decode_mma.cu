@@ -408,10 +408,16 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   const int workers = gridDim.x * C::kWarps;
   const bool fixed_rounds = prefix_local && lds32(kPrefixAddr + 4 * (kPrefixMax - 1)) != 0u;
   int next_item = warp * gridDim.x + blockIdx.x;
-  for (int guard = 0; guard < (1 << 24); ++guard) {        // bounded: never spins
-    const int64_t item = __shfl_sync(0xffffffffu, next_item, 0);
-    if (item >= items_live) break;
-    const int kvh = (int)(item % p.Hkv);
+
+  // One work item: a chunk of one kv head of one sequence.
+  struct Item {
+    int b, kvh, chunk, tok0, tok1;
+    bool valid;
+  };
+  auto decode_item = [&](int64_t item) -> Item {
+    Item x{0, 0, 0, 0, 0, false};
+    if (item >= items_live) return x;
+    x.kvh = (int)(item % p.Hkv);
     const int flat = (int)(item / p.Hkv);                   // chunk number over all sequences
     int lo = 0, hi = p.B;                                   // last b with prefix[b] <= flat
     while (hi - lo > 1) {
@@ -419,19 +425,79 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
       if (prefix_at(mid) <= flat) lo = mid;
       else hi = mid;
     }
-    const int b = lo;
-    const int chunk = flat - prefix_at(b);
-    int L = p.seq_lens[b];
+    x.b = lo;
+    x.chunk = flat - prefix_at(lo);
+    int L = p.seq_lens[lo];
     if (L > p.max_pages * S) {
       L = p.max_pages * S;
       if (p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
     }
-    const int tok0 = chunk * chunk_tokens;
-    const int tok1 = min(L, tok0 + chunk_tokens);
-    if (tok0 >= tok1) {                  // cannot happen with a consistent prefix; stay safe
-      if (lane == 0) next_item = fixed_rounds ? next_item + workers : workers + atomicAdd(p.work_counter, 1);
-      continue;
+    x.tok0 = x.chunk * chunk_tokens;
+    x.tok1 = min(L, x.tok0 + chunk_tokens);
+    x.valid = x.tok0 < x.tok1;
+    // (an empty chunk cannot be numbered by a consistent prefix; if it happens
+    // the warp stops and says so rather than guess)
+    if (!x.valid && p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+    return x;
+  };
+
+  // Copies of window `it` of item `x` into half `buf` of the ring: a tile's key
+  // rows and value rows are contiguous in HBM (16 rows of NB bytes); lane l
+  // moves 16-byte chunks l, l+32, ...; lanes 0..3 also move the norms.  Returns
+  // a bit per tile: set when the tile's page id was inside the pool.  Always
+  // commits one group.
+  auto issue = [&](const Item &x, int it, int buf) -> uint32_t {
+    uint32_t loaded = 0;
+    const int32_t *table = p.page_table + (int64_t)x.b * p.table_stride;
+#pragma unroll
+    for (int u = 0; u < kTilesPerIter; ++u) {
+      const int tok = x.tok0 + it * kIterTokens + u * kTileTokens;
+      if (x.valid && tok < x.tok1) {
+        const int sub = tok & (S - 1);                     // first slot of the tile
+        const int pid = table[tok >> s_shift];
+        if (pid >= 0 && pid < p.P) {
+          loaded |= 1u << u;
+          const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
+          const uint8_t *ks = p.k.pages + (int64_t)x.kvh * p.k.head_stride +
+                              (int64_t)pid * p.k.page_stride + (sub * C::NBK + lane * 16);
+          const uint8_t *vs = p.v.pages + (int64_t)x.kvh * p.v.head_stride +
+                              (int64_t)pid * p.v.page_stride + (sub * C::NBV + lane * 16);
+#pragma unroll
+          for (int i = 0; i < C::NBK / 32; ++i) cp_async16(dst + lane * 16 + i * 512, ks + i * 512);
+#pragma unroll
+          for (int i = 0; i < C::NBV / 32; ++i) {
+            if constexpr (BWV == 4)      // chunk c -> padded row c/4, quarter c%4
+              cp_async16(dst + C::kOffV + (g + 8 * i) * C::kVRow + t * 16, vs + i * 512);
+            else
+              cp_async16(dst + C::kOffV + lane * 16 + i * 512, vs + i * 512);
+          }
+          if (lane < 2)
+            cp_async16(dst + C::kOffNK + lane * 16,
+                       p.k.norms + (int64_t)x.kvh * p.k.norm_head_stride +
+                           (int64_t)pid * p.k.norm_page_stride + sub + lane * 8);
+          else if (lane < 4)
+            cp_async16(dst + C::kOffNV + (lane - 2) * 16,
+                       p.v.norms + (int64_t)x.kvh * p.v.norm_head_stride +
+                           (int64_t)pid * p.v.norm_page_stride + sub + (lane - 2) * 8);
+        } else if (p.status && lane == 0) {
+          atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+        }
+      }
     }
+    cp_async_commit();
+    return loaded;
+  };
+
+  // The ring is used as two halves; `windows` counts the windows this warp has
+  // consumed, across items: the first window of the next item is requested
+  // during the last window of the current one, so a new item starts on data
+  // that is already on its way.
+  Item cur = decode_item(__shfl_sync(0xffffffffu, next_item, 0));
+  uint32_t loaded_next = issue(cur, 0, 0);
+  int windows = 0;
+  for (int guard = 0; guard < (1 << 24) && cur.valid; ++guard) {   // bounded: never spins
+    const int b = cur.b, kvh = cur.kvh, chunk = cur.chunk, tok0 = cur.tok0, tok1 = cur.tok1;
+    Item nxt{0, 0, 0, 0, 0, false};
 
     // ---- query fragments: head g, coordinates 32t .. 32t+31 ----------------
     uint32_t qf[8][2];
@@ -452,63 +518,17 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     const int n_iter = (tok1 - tok0 + kIterTokens - 1) / kIterTokens;
-    const uint8_t *k_head = p.k.pages + (int64_t)kvh * p.k.head_stride;
-    const uint8_t *v_head = p.v.pages + (int64_t)kvh * p.v.head_stride;
-    const __half *nk_head = p.k.norms + (int64_t)kvh * p.k.norm_head_stride;
-    const __half *nv_head = p.v.norms + (int64_t)kvh * p.v.norm_head_stride;
-    const int32_t *table = p.page_table + (int64_t)b * p.table_stride;
-
-    // Copies of one iteration into half `buf` of the ring: a tile's key rows
-    // and value rows are contiguous in HBM (16 rows of NB bytes); lane l moves
-    // 16-byte chunks l, l+32, ...; lanes 0..3 also move the norms.  Returns a
-    // bit per tile: set when the tile's page id was inside the pool.
-    auto issue = [&](int it, int buf) -> uint32_t {
-      uint32_t loaded = 0;
-      if (it < n_iter) {
-#pragma unroll
-        for (int u = 0; u < kTilesPerIter; ++u) {
-          const int tok = tok0 + it * kIterTokens + u * kTileTokens;
-          if (tok < tok1) {
-            const int sub = tok & (S - 1);                     // first slot of the tile
-            const int pid = table[tok >> s_shift];
-            if (pid >= 0 && pid < p.P) {
-              loaded |= 1u << u;
-              const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-              const uint8_t *ks = k_head + (int64_t)pid * p.k.page_stride + (sub * C::NBK + lane * 16);
-              const uint8_t *vs = v_head + (int64_t)pid * p.v.page_stride + (sub * C::NBV + lane * 16);
-#pragma unroll
-              for (int i = 0; i < C::NBK / 32; ++i)
-                cp_async16(dst + lane * 16 + i * 512, ks + i * 512);
-#pragma unroll
-              for (int i = 0; i < C::NBV / 32; ++i) {
-                if constexpr (BWV == 4)      // chunk c -> padded row c/4, quarter c%4
-                  cp_async16(dst + C::kOffV + (g + 8 * i) * C::kVRow + t * 16, vs + i * 512);
-                else
-                  cp_async16(dst + C::kOffV + lane * 16 + i * 512, vs + i * 512);
-              }
-              if (lane < 2)
-                cp_async16(dst + C::kOffNK + lane * 16,
-                           nk_head + (int64_t)pid * p.k.norm_page_stride + sub + lane * 8);
-              else if (lane < 4)
-                cp_async16(dst + C::kOffNV + (lane - 2) * 16,
-                           nv_head + (int64_t)pid * p.v.norm_page_stride + sub + (lane - 2) * 8);
-            } else if (p.status && lane == 0) {
-              atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
-            }
-          }
-        }
-      }
-      cp_async_commit();
-      return loaded;
-    };
-
-    uint32_t loaded_next = issue(0, 0);
     for (int it = 0; it < n_iter; ++it) {
-      const int buf = it & 1;
+      const int buf = windows & 1;
       if (it == (n_iter > 1 ? n_iter - 2 : 0) && lane == 0)
         next_item = fixed_rounds ? next_item + workers : workers + atomicAdd(p.work_counter, 1);
       const uint32_t loaded = loaded_next;
-      loaded_next = issue(it + 1, buf ^ 1);
+      if (it + 1 < n_iter) {
+        loaded_next = issue(cur, it + 1, buf ^ 1);
+      } else {
+        nxt = decode_item(__shfl_sync(0xffffffffu, next_item, 0));
+        loaded_next = issue(nxt, 0, buf ^ 1);
+      }
       cp_async_wait<1>();
       __syncwarp();
 
@@ -598,8 +618,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
         value_mmas<BWV, C::kVRow>(slot + C::kOffV, g, t, sel_v, pb0, pb1, acc);
       }
       __syncwarp();       // every lane is done with this half before it is refilled
+      ++windows;
     }
-    cp_async_wait<0>();
 
     // ---- partial state of this chunk ---------------------------------------
 #pragma unroll
@@ -621,7 +641,9 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
         }
       }
     }
+    cur = nxt;
   }
+  cp_async_wait<0>();
 }
 
 // Merge of the chunk states of `hpb` query heads of one (sequence, kv head)
