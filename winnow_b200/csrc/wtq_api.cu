@@ -68,34 +68,45 @@ extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pag
   const int64_t max_tokens = (int64_t)max_pages * S;
   const int warps = mma_warps_per_sm(bw_k, bw_v);
   if (D == 128 && warps > 0 && S >= 16 && (S & (S - 1)) == 0 && Hq / Hkv <= 8) {
-    // tensor-core path: every warp of the persistent grid should see
-    // about three chunks (upper bound: every sequence at full table width)
+    // tensor-core path.  Every warp of the persistent grid is a worker and
+    // takes whole chunks; a step costs about rounds * (chunk + 34) token
+    // times, where 34 tokens stand for the fixed cost of a chunk (its partial
+    // state written and merged) and `rounds` lies half way between
+    // items / workers and that ratio rounded up: warps of one SM share its
+    // throughput, so a part-filled last round costs less than a full one but
+    // is not free.  Measured on B200, the best chunk is the one that fills
+    // the last round (items just under a multiple of the workers); the search
+    // below finds it.  Lengths are taken at the table's full width.  A chunk
+    // above 512 tokens leaves one warp running long after the others.
     const int64_t workers = (int64_t)device_sms() * warps;
-    int64_t chunk = (max_tokens * groups + 3 * workers - 1) / (3 * workers);
-    chunk = (chunk + 63) / 64 * 64;
-    // a chunk above 512 tokens would leave one warp running long after the
-    // others are done; below 256 the partial states start to cost
-    if (chunk < 256) chunk = 256;
-    if (chunk > 512) chunk = 512;
-    // ... unless the whole step is so small (few kv heads per GPU, short
-    // batches) that 256-token chunks would not even give every warp one item:
-    // then the chunk shrinks, down to 64 tokens, until there are about two
-    // items per warp
-    const int64_t items = groups * ((max_tokens + chunk - 1) / chunk);
-    if (items < 2 * workers) {
-      int64_t small = (max_tokens * groups + 2 * workers - 1) / (2 * workers);
-      small = (small + 31) / 32 * 32;
-      if (small < 64) small = 64;
-      if (small < chunk) chunk = small;
+    int64_t lo = ((max_tokens + kMaxSplits - 1) / kMaxSplits + 31) / 32 * 32;
+    if (lo < 64) lo = 64;
+    int64_t hi = lo > 512 ? lo : 512;
+    int64_t best = hi;
+    double best_cost = 0;
+    for (int64_t chunk = hi; chunk >= lo; chunk -= 32) {
+      const int64_t items = groups * ((max_tokens + chunk - 1) / chunk);
+      const double frac = (double)items / (double)workers;
+      const double rounds = 0.5 * (frac + (double)((items + workers - 1) / workers));
+      const double cost = rounds * (double)(chunk + 34);
+      if (chunk == hi || cost < best_cost) { best = chunk; best_cost = cost; }
     }
-    if (chunk * kMaxSplits < max_tokens) chunk = ((max_tokens + kMaxSplits - 1) / kMaxSplits + 63) / 64 * 64;
-    int64_t splits = (max_tokens + chunk - 1) / chunk;
+    int64_t splits = (max_tokens + best - 1) / best;
     if (splits > kMaxSplits) splits = kMaxSplits;
     return splits < 1 ? 1 : (int)splits;
   }
   // generic path: about eight 128-thread blocks per SM
   const int64_t want = (int64_t)device_sms() * 8;
   return clamp_splits((int)((want + groups - 1) / groups), max_pages, S);
+}
+
+static size_t workspace_for(int B, int Hq, int Hkv, int D, int splits) {
+  const size_t rows = (size_t)B * Hq;
+  size_t bytes = wtq_decode_counter_bytes(B, Hkv);
+  bytes += round_up(rows * D * sizeof(float), 256);                   // rotated query
+  bytes += round_up(rows * splits * D * sizeof(float), 256);          // partial acc
+  bytes += 2 * round_up(rows * splits * sizeof(float), 256);          // partial m, l
+  return bytes;
 }
 
 extern "C" size_t wtq_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_pages, int S,
@@ -105,16 +116,17 @@ extern "C" size_t wtq_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int 
   if (num_splits > 0) {
     splits = clamp_splits(num_splits, max_pages, S);
   } else {                       // whichever kernel the call will pick, it fits
-    const int a = wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 4, 4);
-    const int b = wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 8, 8);
-    splits = a > b ? a : b;
+    splits = 1;
+    for (int bw : {4, 6, 8}) {
+      const int a = wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, bw, bw);
+      if (a > splits) splits = a;
+    }
+    const int a = wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 4, 6);
+    if (a > splits) splits = a;
+    const int g = wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, 3, 3);
+    if (g > splits) splits = g;
   }
-  const size_t rows = (size_t)B * Hq;
-  size_t bytes = wtq_decode_counter_bytes(B, Hkv);
-  bytes += round_up(rows * D * sizeof(float), 256);                   // rotated query
-  bytes += round_up(rows * splits * D * sizeof(float), 256);          // partial acc
-  bytes += 2 * round_up(rows * splits * sizeof(float), 256);          // partial m, l
-  return bytes;
+  return workspace_for(B, Hq, Hkv, D, splits);
 }
 
 static int decode_common(const void *q, int dtype, const int64_t q_strides[2], void *out,
@@ -144,7 +156,7 @@ static int decode_common(const void *q, int dtype, const int64_t q_strides[2], v
   const int splits = num_splits > 0 ? clamp_splits(num_splits, max_pages, S)
                                     : wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S,
                                                              k_side->bw, v_side->bw);
-  const size_t need = wtq_decode_workspace_bytes(B, Hq, Hkv, D, max_pages, S, splits);
+  const size_t need = workspace_for(B, Hq, Hkv, D, splits);
   if (workspace_bytes < need)
     return fail(WTQ_ERR_WORKSPACE, "wtq_decode: workspace %zu < %zu bytes", workspace_bytes, need);
 

@@ -446,6 +446,11 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   // moves 16-byte chunks l, l+32, ...; lanes 0..3 also move the norms.  Returns
   // a bit per tile: set when the tile's page id was inside the pool.  Always
   // commits one group.
+  // Page ids reach the copies through registers: lane l holds entry
+  // block + l of the page table row of sequence block_b, so that a window
+  // costs a shuffle, not a dependent global load, and the table is read once
+  // per 32 pages.
+  int block_b = -1, block_first = 0, block_ids = -1;
   auto issue = [&](const Item &x, int it, int buf) -> uint32_t {
     uint32_t loaded = 0;
     const int32_t *table = p.page_table + (int64_t)x.b * p.table_stride;
@@ -454,7 +459,13 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
       const int tok = x.tok0 + it * kIterTokens + u * kTileTokens;
       if (x.valid && tok < x.tok1) {
         const int sub = tok & (S - 1);                     // first slot of the tile
-        const int pid = table[tok >> s_shift];
+        const int page = tok >> s_shift;
+        if (x.b != block_b || (page & ~31) != block_first) {      // warp-uniform
+          block_b = x.b;
+          block_first = page & ~31;
+          block_ids = block_first + lane < p.max_pages ? table[block_first + lane] : -1;
+        }
+        const int pid = __shfl_sync(0xffffffffu, block_ids, page & 31);
         if (pid >= 0 && pid < p.P) {
           loaded |= 1u << u;
           const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
@@ -532,91 +543,111 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
       cp_async_wait<1>();
       __syncwarp();
 
-      // ---- scores of the tiles ----------------------------------------------
-      float s[kTilesPerIter][4];
-      bool ok[kTilesPerIter][2];
-      float big = 0.f;
-#pragma unroll
-      for (int u = 0; u < kTilesPerIter; ++u) {
-        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-        const int tok = tok0 + it * kIterTokens + u * kTileTokens;
-        const bool page_ok = (loaded >> u) & 1u;
-        ok[u][0] = page_ok && tok + g < tok1;
-        ok[u][1] = page_ok && tok + g + 8 < tok1;
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        key_mmas<BWK>(slot, g, t, sel_k, qf, c);
-        const float nk0 = lds_half(slot + C::kOffNK + g * 2);
-        const float nk1 = lds_half(slot + C::kOffNK + (g + 8) * 2);
-        c[0] *= nk0; c[1] *= nk0; c[2] *= nk1; c[3] *= nk1;
-        big = fmaxf(big, ok[u][0] ? fmaxf(fabsf(c[0]), fabsf(c[1])) : 0.f);
-        big = fmaxf(big, ok[u][1] ? fmaxf(fabsf(c[2]), fabsf(c[3])) : 0.f);
-        s[u][0] = ok[u][0] ? c[0] : -INFINITY;
-        s[u][1] = ok[u][0] ? c[1] : -INFINITY;
-        s[u][2] = ok[u][1] ? c[2] : -INFINITY;
-        s[u][3] = ok[u][1] ? c[3] : -INFINITY;
-      }
-
-      // ---- fp16 operands carry about 2^-11.5 of the score scale as error; when
-      // any score of this window is large (|s| > 8 in log2 units) its tiles are
-      // scored again in fp32 on the CUDA cores, so that large logits cost time,
-      // not accuracy.
-      if (__any_sync(0xffffffffu, big > kPreciseAbove)) {
-        const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
-        const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
-        const float *qa = q0 + (h0 ? 2 * t : 0) * 128, *qb = q0 + (h1 ? 2 * t + 1 : 0) * 128;
+      // A window whose 32 tokens all exist on pages that were found needs no
+      // masks; only the last window of a sequence (or a bad page id) takes the
+      // masked form of the same code.
+      const bool whole = loaded == (1u << kTilesPerIter) - 1u &&
+                         tok0 + (it + 1) * kIterTokens <= tok1;
+      auto window = [&](auto masked_c) {
+        constexpr bool MASKED = decltype(masked_c)::value;
+        // ---- scores of the tiles --------------------------------------------
+        float s[kTilesPerIter][4];
+        bool ok[kTilesPerIter][2];
+        float big = 0.f;
 #pragma unroll
         for (int u = 0; u < kTilesPerIter; ++u) {
           const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-          const float4 d = precise_scores<BWK>(slot, slot + C::kOffNK, g, qa, qb, p.k.centroids);
-          s[u][0] = ok[u][0] ? (h0 ? d.x : 0.f) : -INFINITY;
-          s[u][1] = ok[u][0] ? (h1 ? d.y : 0.f) : -INFINITY;
-          s[u][2] = ok[u][1] ? (h0 ? d.z : 0.f) : -INFINITY;
-          s[u][3] = ok[u][1] ? (h1 ? d.w : 0.f) : -INFINITY;
+          float c[4] = {0.f, 0.f, 0.f, 0.f};
+          key_mmas<BWK>(slot, g, t, sel_k, qf, c);
+          const float nk0 = lds_half(slot + C::kOffNK + g * 2);
+          const float nk1 = lds_half(slot + C::kOffNK + (g + 8) * 2);
+          c[0] *= nk0; c[1] *= nk0; c[2] *= nk1; c[3] *= nk1;
+          if constexpr (MASKED) {
+            const int tok = tok0 + it * kIterTokens + u * kTileTokens;
+            const bool page_ok = (loaded >> u) & 1u;
+            ok[u][0] = page_ok && tok + g < tok1;
+            ok[u][1] = page_ok && tok + g + 8 < tok1;
+            big = fmaxf(big, ok[u][0] ? fmaxf(fabsf(c[0]), fabsf(c[1])) : 0.f);
+            big = fmaxf(big, ok[u][1] ? fmaxf(fabsf(c[2]), fabsf(c[3])) : 0.f);
+            s[u][0] = ok[u][0] ? c[0] : -INFINITY;
+            s[u][1] = ok[u][0] ? c[1] : -INFINITY;
+            s[u][2] = ok[u][1] ? c[2] : -INFINITY;
+            s[u][3] = ok[u][1] ? c[3] : -INFINITY;
+          } else {
+            ok[u][0] = ok[u][1] = true;
+            big = fmaxf(big, fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3]))));
+            s[u][0] = c[0]; s[u][1] = c[1]; s[u][2] = c[2]; s[u][3] = c[3];
+          }
         }
-      }
 
-      // ---- running max per head (heads 2t, 2t+1), shared over the 8 rows ----
-      float mx[2] = {m_run[0], m_run[1]};
+        // ---- fp16 operands carry about 2^-11.5 of the score scale as error;
+        // when any score of this window is large (|s| > 8 in log2 units) its
+        // tiles are scored again in fp32 on the CUDA cores, so that large logits
+        // cost time, not accuracy.
+        if (__any_sync(0xffffffffu, big > kPreciseAbove)) {
+          const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
+          const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
+          const float *qa = q0 + (h0 ? 2 * t : 0) * 128, *qb = q0 + (h1 ? 2 * t + 1 : 0) * 128;
 #pragma unroll
-      for (int u = 0; u < kTilesPerIter; ++u) {
-        mx[0] = fmaxf(mx[0], fmaxf(s[u][0], s[u][2]));
-        mx[1] = fmaxf(mx[1], fmaxf(s[u][1], s[u][3]));
-      }
-#pragma unroll
-      for (int o = 4; o < 32; o <<= 1) {
-        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
-        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
-      }
-      // exp2(-inf - -inf) is defined as 0: with nothing seen the base is 0
-      const float base0 = mx[0] == -INFINITY ? 0.f : mx[0];
-      const float base1 = mx[1] == -INFINITY ? 0.f : mx[1];
-      const float alpha0 = ex2(m_run[0] - base0), alpha1 = ex2(m_run[1] - base1);
-      if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          acc[j][0] *= alpha0; acc[j][1] *= alpha1; acc[j][2] *= alpha0; acc[j][3] *= alpha1;
+          for (int u = 0; u < kTilesPerIter; ++u) {
+            const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
+            const float4 d = precise_scores<BWK>(slot, slot + C::kOffNK, g, qa, qb, p.k.centroids);
+            s[u][0] = ok[u][0] ? (h0 ? d.x : 0.f) : -INFINITY;
+            s[u][1] = ok[u][0] ? (h1 ? d.y : 0.f) : -INFINITY;
+            s[u][2] = ok[u][1] ? (h0 ? d.z : 0.f) : -INFINITY;
+            s[u][3] = ok[u][1] ? (h1 ? d.w : 0.f) : -INFINITY;
+          }
         }
-        l_run[0] *= alpha0;
-        l_run[1] *= alpha1;
-      }
-      m_run[0] = mx[0];
-      m_run[1] = mx[1];
 
-      // ---- values of the tiles ----------------------------------------------
+        // ---- running max per head (heads 2t, 2t+1), shared over the 8 rows --
+        float mx[2] = {m_run[0], m_run[1]};
 #pragma unroll
-      for (int u = 0; u < kTilesPerIter; ++u) {
-        const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-        const float nv0 = lds_half(slot + C::kOffNV + g * 2);
-        const float nv1 = lds_half(slot + C::kOffNV + (g + 8) * 2);
-        const float p0 = ex2(s[u][0] - base0), p1 = ex2(s[u][1] - base1);
-        const float p2 = ex2(s[u][2] - base0), p3 = ex2(s[u][3] - base1);
-        l_run[0] += p0 + p2;
-        l_run[1] += p1 + p3;
-        // rows g / g+8 of P' (token x head) -> B fragment (token pairs of head g)
-        const uint32_t pb0 = movmatrix_trans(ok[u][0] ? pack_half2(p0 * nv0, p1 * nv0) : 0u);
-        const uint32_t pb1 = movmatrix_trans(ok[u][1] ? pack_half2(p2 * nv1, p3 * nv1) : 0u);
-        value_mmas<BWV, C::kVRow>(slot + C::kOffV, g, t, sel_v, pb0, pb1, acc);
-      }
+        for (int u = 0; u < kTilesPerIter; ++u) {
+          mx[0] = fmaxf(mx[0], fmaxf(s[u][0], s[u][2]));
+          mx[1] = fmaxf(mx[1], fmaxf(s[u][1], s[u][3]));
+        }
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+        }
+        // exp2(-inf - -inf) is defined as 0: with nothing seen the base is 0
+        const float base0 = mx[0] == -INFINITY ? 0.f : mx[0];
+        const float base1 = mx[1] == -INFINITY ? 0.f : mx[1];
+        const float alpha0 = ex2(m_run[0] - base0), alpha1 = ex2(m_run[1] - base1);
+        if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[j][0] *= alpha0; acc[j][1] *= alpha1; acc[j][2] *= alpha0; acc[j][3] *= alpha1;
+          }
+          l_run[0] *= alpha0;
+          l_run[1] *= alpha1;
+        }
+        m_run[0] = mx[0];
+        m_run[1] = mx[1];
+
+        // ---- values of the tiles --------------------------------------------
+#pragma unroll
+        for (int u = 0; u < kTilesPerIter; ++u) {
+          const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
+          const float nv0 = lds_half(slot + C::kOffNV + g * 2);
+          const float nv1 = lds_half(slot + C::kOffNV + (g + 8) * 2);
+          const float p0 = ex2(s[u][0] - base0), p1 = ex2(s[u][1] - base1);
+          const float p2 = ex2(s[u][2] - base0), p3 = ex2(s[u][3] - base1);
+          l_run[0] += p0 + p2;
+          l_run[1] += p1 + p3;
+          // rows g / g+8 of P' (token x head) -> B fragment (token pairs of head g)
+          uint32_t r0 = pack_half2(p0 * nv0, p1 * nv0), r1 = pack_half2(p2 * nv1, p3 * nv1);
+          if constexpr (MASKED) {
+            r0 = ok[u][0] ? r0 : 0u;
+            r1 = ok[u][1] ? r1 : 0u;
+          }
+          const uint32_t pb0 = movmatrix_trans(r0), pb1 = movmatrix_trans(r1);
+          value_mmas<BWV, C::kVRow>(slot + C::kOffV, g, t, sel_v, pb0, pb1, acc);
+        }
+      };
+      if (whole) window(std::false_type{});
+      else window(std::true_type{});
       __syncwarp();       // every lane is done with this half before it is refilled
       ++windows;
     }
@@ -912,7 +943,11 @@ int mma_chunk_tokens(int max_tokens, int splits) {
 template <int BWK, int BWV>
 static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cudaStream_t stream) {
   using C = Cfg<BWK, BWV>;
-  static bool opted_in = false;
+  // function attributes belong to the device the call runs on
+  static bool opted_in_dev[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  bool &opted_in = opted_in_dev[dev & 63];
   if (!opted_in) {
     cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<BWK, BWV>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
