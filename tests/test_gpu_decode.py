@@ -300,3 +300,70 @@ def test_more_sequences_than_the_shared_prefix_holds():
     for b, L in enumerate(lens):
         if L == 0:
             assert (got[b] == 0).all()
+
+
+@pytest.mark.parametrize("name", ["val_long", "val_edges", "mixed_4k_6v"])
+def test_exchange_epilogue_with_two_ranks_on_one_gpu(name):
+    """`wtq_decode_exchange` for two ranks whose buffers both live on this GPU:
+    the ranks' calls run one after the other on one stream (so no kernel ever
+    waits for a kernel that has not been launched), each stores its head rows
+    into both ranks' buffers and publishes its step; after both, each rank's
+    bounded wait finds every flag set and both buffers hold the full output."""
+    import ctypes
+    from winnow_b200 import _lib, tp
+    from winnow_b200.packed_attention_cuda import DecodePlan
+    c = next((x for x in cases.ATTENTION_CASES if x.name == name), None)
+    if c is None or c.Hkv % 2:
+        pytest.skip("case not present or kv heads do not split in two")
+    q, okv, _ = oracle_case(c)
+    scale = orc.default_scale(c.D)
+    dev = torch.device("cuda", 0)
+    kv = to_device(okv, dev)
+    world, B, D = 2, q.shape[0], c.D
+    el = q.element_size()
+    bufs = [[torch.zeros(B, c.Hq, 1, D, dtype=q.dtype, device=dev) for _ in range(2)]
+            for _ in range(world)]                      # [rank][parity]
+    flags = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
+    peer_out = [torch.tensor([bufs[r][i].data_ptr() for r in range(world)], dtype=torch.int64,
+                             device=dev) for i in range(2)]
+    peer_flags = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
+    lib = _lib.lib()
+    ranks = []
+    for rank in range(world):
+        qs, ks = tp.head_shard(rank, world, c.Hq, c.Hkv)
+        shard = pa.PackedKV(kv.k_pages[:, ks].contiguous(), kv.k_norms[:, ks].contiguous(),
+                            kv.v_pages[:, ks].contiguous(), kv.v_norms[:, ks].contiguous(),
+                            kv.page_table, kv.seq_lens, kv.k_quant, kv.v_quant, kv.head_dim)
+        q_local = q[:, qs].contiguous().to(dev)
+        hq = q_local.shape[1]
+        plan = DecodePlan(q_local, shard, scale, out=bufs[rank][0][:, :hq])
+        try:
+            plan.run_exchange(None, dry_run=True)
+        except _lib.BackendError:
+            pytest.skip("shape has no exchange epilogue")
+        ex = _lib.Exchange()
+        ex.peer_out[0], ex.peer_out[1] = peer_out[0].data_ptr(), peer_out[1].data_ptr()
+        ex.peer_flags = peer_flags.data_ptr()
+        ex.out_strides[0], ex.out_strides[1] = bufs[0][0].stride(0), bufs[0][0].stride(1)
+        ex.rank, ex.world, ex.head_offset = rank, world, rank * hq
+        step = torch.zeros(1, dtype=torch.int32, device=dev)
+        done = torch.zeros(1, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ex.step_counter, ex.done_counter = step.data_ptr(), done.data_ptr()
+        ranks.append((plan, ex, step, done, status, q_local, qs))
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    for call in (1, 2, 3):                               # parity 1, 0, 1 of the double buffer
+        qi = q * (1.0 + 0.5 * (call - 1))
+        for plan, ex, *_rest, q_local, qs in ranks:
+            q_local.copy_(qi[:, qs])
+            plan.run_exchange(ex)
+        for rank, (plan, ex, step, done, status, *_r) in enumerate(ranks):
+            _lib.check(lib.wtq_exchange_wait(flags[rank].data_ptr(), world, step.data_ptr(),
+                                             1000, status.data_ptr(), stream))
+        torch.cuda.synchronize()
+        ref = orc.tiled_attention(qi, okv, scale)
+        for rank, (plan, ex, step, done, status, *_r) in enumerate(ranks):
+            assert int(status.item()) == 0
+            assert int(step.item()) == call and int(done.item()) == 0
+            assert flags[rank].tolist() == [call] * world
+            assert_attention_close(bufs[rank][call & 1].float().cpu(), ref)

@@ -398,15 +398,22 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
-  // Work is handed out dynamically: item i (one chunk of one kv head of one
-  // sequence; only chunks that exist are numbered) goes to the next free warp.
-  // Every warp starts on the item with its own number (consecutive items go to
-  // different CTAs); later items come from the queue.  The next item is
-  // requested one window before the current one ends: its round trip is hidden
-  // and the requests of different warps are spread in time.
+  // Items (one chunk of one kv head of one sequence; only chunks that exist are
+  // numbered) are dealt round-robin, consecutive items to different CTAs; when
+  // the sequences differ in length the last rounds come from a queue in global
+  // memory instead, so that the warps finish together.  A queue item is
+  // requested one window before the current item ends: its round trip is
+  // hidden and the requests of different warps are spread in time.
   const int64_t items_live = (int64_t)prefix_at(p.B) * p.Hkv;
   const int workers = gridDim.x * C::kWarps;
   const bool fixed_rounds = prefix_local && lds32(kPrefixAddr + 4 * (kPrefixMax - 1)) != 0u;
+  // Ragged batches: items differ only in each sequence's last chunk, so all
+  // rounds but the last two are dealt round-robin as well (no queue traffic,
+  // no round trip); the queue hands out the rest and evens out the end.
+  const int static_rounds =
+      fixed_rounds ? 0x7fffffff : max(1, (int)min(items_live / workers, (int64_t)0x7fffffff) - 1);
+  const int queue_base = fixed_rounds ? 0 : static_rounds * workers;
+  int taken = 1;                                      // items this warp has been dealt
   int next_item = warp * gridDim.x + blockIdx.x;
 
   // One work item: a chunk of one kv head of one sequence.
@@ -532,7 +539,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     for (int it = 0; it < n_iter; ++it) {
       const int buf = windows & 1;
       if (it == (n_iter > 1 ? n_iter - 2 : 0) && lane == 0)
-        next_item = fixed_rounds ? next_item + workers : workers + atomicAdd(p.work_counter, 1);
+        next_item = taken++ < static_rounds ? next_item + workers
+                                            : queue_base + atomicAdd(p.work_counter, 1);
       const uint32_t loaded = loaded_next;
       if (it + 1 < n_iter) {
         loaded_next = issue(cur, it + 1, buf ^ 1);
