@@ -426,12 +426,110 @@ __global__ void __launch_bounds__(kRotThreads) rotate_q_rows_kernel(
   }
 }
 
+// head_dim 128, the shape of the tensor-core path: the same sums in the same
+// order as rotate_q_rows_kernel with everything a compile-time constant, the
+// next group's query rows requested before the current group's arithmetic
+// (their round trip is hidden) and two barriers per group instead of three
+// (the staging buffer alternates).
+template <int NR>
+__global__ void __launch_bounds__(kRotThreads) rotate_q128_kernel(
+    const void *q, int dtype, int64_t qsb, int64_t qsh, const float *Pi, float mult, int Hq,
+    int total_rows, float *q_rot, const int32_t *seq_lens, int B, int chunk_tokens,
+    int max_tokens, int32_t *chunk_prefix) {
+  __shared__ __align__(16) float qs[2][128][NR];       // [buffer][coordinate][row]
+  __shared__ float part_s[3][NR][128];
+  if (chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
+    write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, chunk_prefix);
+  const int tid = threadIdx.x, col = tid & 127, quarter = tid >> 7;
+  float4 held[8];                                       // this thread's quarter of row `col` of Pi
+  {
+    const float4 *row = reinterpret_cast<const float4 *>(Pi + col * 128 + quarter * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) held[j] = __ldg(row + j);
+  }
+  constexpr int PER = NR * 128 / kRotThreads;           // query elements a thread stages
+  static_assert(PER >= 1, "at least four rows per group");
+  float pre[PER];
+  auto fetch = [&](int grp) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = tid + i * kRotThreads;
+      const int row = grp * NR + (e >> 7);
+      float v = 0.f;
+      if (row < total_rows) {
+        const int b = row / Hq, h = row - b * Hq;
+        v = load_as_float(q, (int64_t)b * qsb + (int64_t)h * qsh + (e & 127), dtype);
+      }
+      pre[i] = v;
+    }
+  };
+  const int groups = (total_rows + NR - 1) / NR;
+  int grp = blockIdx.x;
+  if (grp < groups) fetch(grp);
+  for (int buf = 0; grp < groups; grp += gridDim.x, buf ^= 1) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = tid + i * kRotThreads;
+      qs[buf][e & 127][e >> 7] = pre[i];
+    }
+    __syncthreads();
+    if (grp == (int)blockIdx.x) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    if (grp + (int)gridDim.x < groups) fetch(grp + gridDim.x);
+    float acc[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float wv[4] = {held[j].x, held[j].y, held[j].z, held[j].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int d = quarter * 32 + 4 * j + k;
+#pragma unroll
+        for (int r4 = 0; r4 < NR; r4 += 4) {
+          const float4 x = *reinterpret_cast<const float4 *>(&qs[buf][d][r4]);
+          acc[r4 + 0] = fmaf(x.x, wv[k], acc[r4 + 0]);
+          acc[r4 + 1] = fmaf(x.y, wv[k], acc[r4 + 1]);
+          acc[r4 + 2] = fmaf(x.z, wv[k], acc[r4 + 2]);
+          acc[r4 + 3] = fmaf(x.w, wv[k], acc[r4 + 3]);
+        }
+      }
+    }
+    if (quarter > 0) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) part_s[quarter - 1][r][col] = acc[r];
+    }
+    __syncthreads();
+    if (quarter == 0) {
+      const int row0 = grp * NR;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const float v = (acc[r] + part_s[0][r][col]) + (part_s[1][r][col] + part_s[2][r][col]);
+        if (row0 + r < total_rows) q_rot[(int64_t)(row0 + r) * 128 + col] = v * mult;
+      }
+    }
+  }
+}
+
 int launch_rotate_q(const void *q, int dtype, const int64_t *qs, const float *Pi, float scale,
                     int B, int Hq, int D, float *q_rot, const int32_t *seq_lens, int chunk_tokens,
                     int max_tokens, int32_t *chunk_prefix, cudaStream_t stream) {
   const int rows = B * Hq;
-  if (D % 16 == 0 && D <= 256 && ((uintptr_t)Pi & 15) == 0)
-    rotate_q_rows_kernel<4><<<std::min((rows + 3) / 4, 2 * 148), kRotThreads, 0, stream>>>(
+  // (two 512-thread blocks of the head_dim-128 kernel fit an SM, one of the general kernel)
+  if (D == 128 && ((uintptr_t)Pi & 15) == 0 && rows >= 8 * 148)
+    rotate_q128_kernel<8><<<std::min((rows + 7) / 8, 2 * 148), kRotThreads, 0, stream>>>(
+        q, dtype, qs[0], qs[1], Pi, scale, Hq, rows, q_rot, seq_lens, B, chunk_tokens, max_tokens,
+        chunk_prefix);
+  else if (D == 128 && ((uintptr_t)Pi & 15) == 0)
+    rotate_q128_kernel<4><<<std::min((rows + 3) / 4, 2 * 148), kRotThreads, 0, stream>>>(
+        q, dtype, qs[0], qs[1], Pi, scale, Hq, rows, q_rot, seq_lens, B, chunk_tokens, max_tokens,
+        chunk_prefix);
+  else if (D % 16 == 0 && D <= 256 && ((uintptr_t)Pi & 15) == 0 && rows >= 8 * 148)
+    // many rows: eight per pass halve the passes of the persistent blocks
+    rotate_q_rows_kernel<8><<<std::min((rows + 7) / 8, 148), kRotThreads, 0, stream>>>(
+        q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
+        max_tokens, chunk_prefix);
+  else if (D % 16 == 0 && D <= 256 && ((uintptr_t)Pi & 15) == 0)
+    rotate_q_rows_kernel<4><<<std::min((rows + 3) / 4, 148), kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
         max_tokens, chunk_prefix);
   else if (rows % 4 == 0)

@@ -893,6 +893,113 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
   }
 }
 
+// The same merge with many small blocks: one 128-thread block per `hpb` query
+// heads of a (sequence, kv head) group (grid = groups x n_rep / hpb), so that an
+// SM holds many blocks at once and their round trips to L2 overlap (the
+// persistent kernel above walks its groups one after the other).  Thread =
+// output coordinate.  Warp w computes the chunk weights of heads w and w + 4 of
+// the block's heads; every thread then sums its coordinate over the chunks,
+// sixteen states in flight; the rotation reads Pi_V through L1, which this
+// kernel leaves large (it holds the 64 KB of Pi_V for every block of the SM).
+// At most kSmallMergeChunks chunks per sequence.
+constexpr int kSmallMergeChunks = 256;
+__global__ void __launch_bounds__(128, 8) merge_small_kernel(MergeParams p, const int32_t *seq_lens,
+                                                          int Hkv, int group_heads, int n_rep,
+                                                          int chunk_tokens, int max_tokens) {
+  __shared__ float w_s[8][kSmallMergeChunks];
+  __shared__ __align__(16) float a_s[128][8];           // [coordinate][head]
+  __shared__ float inv_s[8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int group = blockIdx.x;
+  const int b = group / Hkv, kvh = group - b * Hkv;
+  const int head0 = kvh * group_heads + blockIdx.y * n_rep;   // n_rep: heads of this block
+  int L = seq_lens[b];
+  L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
+  const int chunks = (L + chunk_tokens - 1) / chunk_tokens;
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");      // partial states are complete
+  if (p.work_counter != nullptr && group == 0 && blockIdx.y == 0 && tid == 0) *p.work_counter = 0;
+  const uint32_t exchange_step = p.world > 0 ? *p.step_counter + 1u : 0u;
+  const int64_t row0 = ((int64_t)b * p.Hq + head0) * p.num_splits;
+  for (int h = warp; h < n_rep; h += 4) {              // weights of head h
+    const int64_t base = row0 + (int64_t)h * p.num_splits;
+    float mv[kSmallMergeChunks / 32], lv[kSmallMergeChunks / 32];
+    float gmax = -INFINITY, denom = 0.f;
+#pragma unroll
+    for (int i = 0; i < kSmallMergeChunks / 32; ++i) {
+      const int c = lane + 32 * i;
+      mv[i] = c < chunks ? __ldcg(p.part_m + base + c) : -INFINITY;
+      lv[i] = c < chunks ? __ldcg(p.part_l + base + c) : 0.f;
+      gmax = fmaxf(gmax, mv[i]);
+    }
+    gmax = warp_max(gmax);
+#pragma unroll
+    for (int i = 0; i < kSmallMergeChunks / 32; ++i) {
+      const int c = lane + 32 * i;
+      const float w = mv[i] == -INFINITY ? 0.f : exp2f(mv[i] - gmax);
+      if (c < chunks) w_s[h][c] = w;
+      denom += w * lv[i];
+    }
+    denom = warp_sum(denom);
+    if (lane == 0) inv_s[h] = denom > 0.f ? 1.f / fmaxf(denom, 1e-30f) : 0.f;
+  }
+  __syncthreads();
+  for (int h = 0; h < n_rep; ++h) {                     // chunk sums of coordinate `tid`
+    const float *src = p.part_acc + (row0 + (int64_t)h * p.num_splits) * 128 + tid;
+    float a = 0.f;
+    for (int c0 = 0; c0 < chunks; c0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = c0 + i < chunks ? __ldcg(src + (int64_t)(c0 + i) * 128) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) a = fmaf(c0 + i < chunks ? w_s[h][c0 + i] : 0.f, v[i], a);
+    }
+    a_s[tid][h] = a * inv_s[h];
+  }
+  for (int h = n_rep; h < 8; ++h) a_s[tid][h] = 0.f;
+  __syncthreads();
+  float o[8];
+#pragma unroll
+  for (int h = 0; h < 8; ++h) o[h] = 0.f;
+  const float *pi = p.Pi_v + tid;
+#pragma unroll 8
+  for (int d = 0; d < 128; ++d) {
+    const float w = __ldg(pi + d * 128);
+    const float4 x = *reinterpret_cast<const float4 *>(&a_s[d][0]);
+    const float4 y = *reinterpret_cast<const float4 *>(&a_s[d][4]);
+    o[0] = fmaf(x.x, w, o[0]); o[1] = fmaf(x.y, w, o[1]);
+    o[2] = fmaf(x.z, w, o[2]); o[3] = fmaf(x.w, w, o[3]);
+    o[4] = fmaf(y.x, w, o[4]); o[5] = fmaf(y.y, w, o[5]);
+    o[6] = fmaf(y.z, w, o[6]); o[7] = fmaf(y.w, w, o[7]);
+  }
+#pragma unroll
+  for (int h = 0; h < 8; ++h) {
+    if (h < n_rep) {
+      if (p.world == 0) {
+        store_from_float(p.out, (int64_t)b * p.osb + (int64_t)(head0 + h) * p.osh + tid, o[h],
+                         p.dtype);
+      } else {                            // the row goes to every rank's full buffer
+        const int64_t at = (int64_t)b * p.osb + (int64_t)(p.head_offset + head0 + h) * p.osh + tid;
+        void *const *dests = p.peer_out[exchange_step & 1u];
+        for (int r = 0; r < p.world; ++r) store_from_float(dests[r], at, o[h], p.dtype);
+      }
+    }
+  }
+  if (p.world > 0) {                      // publish, as in merge_group_kernel
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      if (atomicAdd(p.done_counter, 1u) == gridDim.x * gridDim.y - 1) {
+        *p.done_counter = 0;
+        *p.step_counter = exchange_step;
+        __threadfence_system();
+        for (int r = 0; r < p.world; ++r)
+          *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = exchange_step;
+        __threadfence_system();
+      }
+    }
+  }
+}
+
 // Waits (bounded) until every slot of the local flag array has reached `step`.
 __global__ void exchange_wait_kernel(const uint32_t *flags, int world, const uint32_t *step_counter,
                                      long long spin_limit, int32_t *status) {
@@ -987,12 +1094,28 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
   cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<BWK, BWV>, p, chunk_tokens);
   profile_mark_end(stream);
   if (e != cudaSuccess) return check_cuda(e, "wtq_decode mma launch");
+  const int num_groups_all = p.B * p.Hkv;
+  if (num_groups_all >= 4 * sms && p.num_splits <= kSmallMergeChunks) {
+    // many groups: small blocks, several resident per SM, all heads of a group
+    // in one block.  (With fewer groups the persistent kernel below is faster,
+    // also against this kernel run with fewer heads per block: measured.)
+    const int heads = p.n_rep;
+    cfg.gridDim = dim3((unsigned)num_groups_all, (unsigned)(p.n_rep / heads));
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    e = cudaLaunchKernelEx(&cfg, merge_small_kernel, m, p.seq_lens, p.Hkv, p.n_rep, heads,
+                           chunk_tokens, max_tokens);
+    note_launches(2);
+    return check_cuda(e, "wtq_decode merge launch");
+  }
   // heads per merge block: all of the group when there are many groups, fewer
   // (down to one) when a handful of long sequences would leave most SMs idle
   int hpb = p.n_rep;
   while (hpb > 1 && hpb % 2 == 0 && (int64_t)p.B * p.Hkv * (p.n_rep / hpb) < sms / 2) hpb /= 2;
   const int num_groups = p.B * p.Hkv;
-  cfg.gridDim = dim3((unsigned)std::min(num_groups, 2 * sms), (unsigned)(p.n_rep / hpb));
+  // one merge block is resident per SM: no more blocks than SMs, each walks its groups
+  const int passes = p.n_rep / hpb;
+  cfg.gridDim = dim3((unsigned)std::min(num_groups, std::max(1, sms / passes)), (unsigned)passes);
   cfg.blockDim = dim3(kMergeThreads);
   cfg.dynamicSmemBytes = 128 * 128 * sizeof(float);
   e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, p.seq_lens, num_groups, p.Hkv, p.n_rep, hpb,
