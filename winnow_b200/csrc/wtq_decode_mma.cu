@@ -718,6 +718,9 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
     }
   }
   asm volatile("griddepcontrol.wait;\n" ::: "memory");      // partial states are complete
+  // (the exchange's wait kernel, if it follows, may be scheduled now: it waits
+  // for this grid to finish before it reads anything)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (p.work_counter != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0)
     *p.work_counter = 0;
   // The first 32 chunk states of a thread's (head, coordinate) are requested one
@@ -887,7 +890,6 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
         __threadfence_system();
         for (int r = 0; r < p.world; ++r)
           *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = exchange_step;
-        __threadfence_system();
       }
     }
   }
@@ -917,6 +919,9 @@ __global__ void __launch_bounds__(128, 8) merge_small_kernel(MergeParams p, cons
   L = L < 0 ? 0 : (L > max_tokens ? max_tokens : L);
   const int chunks = (L + chunk_tokens - 1) / chunk_tokens;
   asm volatile("griddepcontrol.wait;\n" ::: "memory");      // partial states are complete
+  // (the exchange's wait kernel, if it follows, may be scheduled now: it waits
+  // for this grid to finish before it reads anything)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (p.work_counter != nullptr && group == 0 && blockIdx.y == 0 && tid == 0) *p.work_counter = 0;
   const uint32_t exchange_step = p.world > 0 ? *p.step_counter + 1u : 0u;
   const int64_t row0 = ((int64_t)b * p.Hq + head0) * p.num_splits;
@@ -994,7 +999,6 @@ __global__ void __launch_bounds__(128, 8) merge_small_kernel(MergeParams p, cons
         __threadfence_system();
         for (int r = 0; r < p.world; ++r)
           *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = exchange_step;
-        __threadfence_system();
       }
     }
   }
@@ -1004,7 +1008,10 @@ __global__ void __launch_bounds__(128, 8) merge_small_kernel(MergeParams p, cons
 __global__ void exchange_wait_kernel(const uint32_t *flags, int world, const uint32_t *step_counter,
                                      long long spin_limit, int32_t *status) {
   const int r = threadIdx.x;
-  const uint32_t step = *step_counter;     // advanced by the merge kernel ahead of this one
+  // launched early (programmatic dependent launch): wait for the merge kernel
+  // ahead of this one, which advances the step counter
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  const uint32_t step = *reinterpret_cast<const volatile uint32_t *>(step_counter);
   if (r < world) {
     const volatile uint32_t *slot = flags + r;
     bool arrived = false;
@@ -1022,9 +1029,19 @@ __global__ void exchange_wait_kernel(const uint32_t *flags, int world, const uin
 
 int launch_exchange_wait(const uint32_t *flags, int world, const uint32_t *step_counter,
                          long long spin_limit, int32_t *status, cudaStream_t stream) {
-  exchange_wait_kernel<<<1, 32, 0, stream>>>(flags, world, step_counter, spin_limit, status);
+  cudaLaunchAttribute pdl;
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = stream;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, exchange_wait_kernel, flags, world, step_counter,
+                                     spin_limit, status);
   note_launches(1);
-  return check_cuda(cudaGetLastError(), "wtq_exchange_wait launch");
+  return check_cuda(e, "wtq_exchange_wait launch");
 }
 
 // Worker warps per SM of the instantiation serving (bw_k, bw_v); 0 when the
