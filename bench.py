@@ -33,6 +33,10 @@ from winnow_b200 import workloads  # noqa: E402
 
 METRIC = "packed_decode_attn_us_per_step"
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the scan kernel
+# over its algorithmic bytes, from an ncu capture of the default workload (its
+# summary is kept under profiles/; the excess is the chunk states it writes)
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 145.5 / 138.7
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -391,7 +395,10 @@ def run_ours(args):
                 "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "frac": achieved / peak, "traffic": alg_rank * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                     "traffic_source": "ncu capture of the scan kernel on config2 (dram read + write "
+                                       "145.5 MB per launch for 138.7 MB algorithmic), scaled by "
+                                       "algorithmic bytes", "peak_kind": peak_kind,
                      "kernel": "page-scan kernel of wtq_decode", "kernel_us": kernel_us,
                      "algorithmic_bytes_per_launch": alg_rank},
         "cpu_baseline": cpu,
