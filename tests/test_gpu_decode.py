@@ -302,7 +302,12 @@ def test_more_sequences_than_the_shared_prefix_holds():
             assert (got[b] == 0).all()
 
 
-@pytest.mark.parametrize("name", ["val_long", "val_edges", "mixed_4k_6v"])
+# 160 sequences x 4 kv heads per rank: enough groups for the small-block merge kernel
+MANY_GROUPS = cases.AttnCase("many_groups", 3001, 160, 32, 8, 128,
+                             tuple(1 + (37 * i) % 90 for i in range(160)), 16, 4, 4)
+
+
+@pytest.mark.parametrize("name", ["val_long", "val_edges", "mixed_4k_6v", "many_groups"])
 def test_exchange_epilogue_with_two_ranks_on_one_gpu(name):
     """`wtq_decode_exchange` for two ranks whose buffers both live on this GPU:
     the ranks' calls run one after the other on one stream (so no kernel ever
@@ -312,7 +317,8 @@ def test_exchange_epilogue_with_two_ranks_on_one_gpu(name):
     import ctypes
     from winnow_b200 import _lib, tp
     from winnow_b200.packed_attention_cuda import DecodePlan
-    c = next((x for x in cases.ATTENTION_CASES if x.name == name), None)
+    c = MANY_GROUPS if name == "many_groups" else next(
+        (x for x in cases.ATTENTION_CASES if x.name == name), None)
     if c is None or c.Hkv % 2:
         pytest.skip("case not present or kv heads do not split in two")
     q, okv, _ = oracle_case(c)
