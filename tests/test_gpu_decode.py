@@ -373,3 +373,38 @@ def test_exchange_epilogue_with_two_ranks_on_one_gpu(name):
             assert int(step.item()) == call and int(done.item()) == 0
             assert flags[rank].tolist() == [call] * world
             assert_attention_close(bufs[rank][call & 1].float().cpu(), ref)
+
+
+@pytest.mark.parametrize("name", ["val_tail", "mixed_4k_6v", "qwen7b_gqa_mixed", "gqa8_2"])
+@pytest.mark.parametrize("Q", [1, 5])
+def test_reference_operator_names_on_the_gpu(name, Q):
+    """`tiled_compressed_attention`, `explicit_compressed_attention` and
+    `reconstruct_attention` keep the reference's names, signatures and fp32
+    result; a chunk of Q query tokens is causal inside the chunk (query i sees
+    the keys up to its own position).  Checked against the CPU oracle."""
+    c = next(x for x in cases.ATTENTION_CASES if x.name == name)
+    q1, okv, _ = oracle_case(c)
+    g = torch.Generator().manual_seed(c.seed + 17)
+    q = torch.randn(q1.shape[0], q1.shape[1], Q, q1.shape[3], generator=g).to(q1.dtype)
+    q = q * float(q1.float().std())
+    scale = orc.default_scale(c.D)
+    ref = orc.tiled_attention(q, okv, scale)
+    assert ref.shape == q.shape
+    dev = torch.device("cuda", 0)
+    kv = to_device(okv, dev)
+    qd = q.to(dev)
+    for fn, kwargs in ((pa.tiled_compressed_attention, {}),
+                       (pa.tiled_compressed_attention, {"split_pages": 3}),
+                       (pa.explicit_compressed_attention, {}),
+                       (pa.reconstruct_attention, {})):
+        got = fn(qd, kv, scale, **kwargs)
+        assert got.dtype == torch.float32 and got.shape == q.shape
+        assert_attention_close(got.cpu(), ref)
+    # rows of a chunk that reach before the start of a short sequence see nothing
+    if Q > 1:
+        lens = okv.seq_lens.tolist()
+        got = pa.tiled_compressed_attention(qd, kv, scale).cpu()
+        for b, L in enumerate(lens):
+            for i in range(Q):
+                if L - (Q - 1 - i) <= 0:
+                    assert float(got[b, :, i].abs().max()) == 0.0

@@ -162,3 +162,48 @@ def test_workload_definitions():
     assert total == 64 and sorted(table[0].tolist()) == list(range(64))
     k, v = workloads.dense_kv(workloads.WORKLOADS["config1"], 0)
     assert k.shape == (2, 1024, 128)
+
+
+def test_merge_partials_and_rotations_follow_the_reference_algebra():
+    """`merge_partials` combines online-softmax states as the oracle's merge
+    does (empty states carry -inf and weigh nothing); `rotate_query` /
+    `rotate_output` are q Pi^T and a Pi."""
+    import torch
+    from oracle import tq_oracle as orc
+    from winnow_b200 import packed_attention as pa
+    g = torch.Generator().manual_seed(5)
+    m1, m2 = torch.randn(2, 3, 1, generator=g), torch.randn(2, 3, 1, generator=g)
+    m2[0, 0, 0] = float("-inf")
+    l1, l2 = torch.rand(2, 3, 1, generator=g) + 0.1, torch.rand(2, 3, 1, generator=g)
+    l2[0, 0, 0] = 0.0
+    a1, a2 = torch.randn(2, 3, 1, 8, generator=g), torch.randn(2, 3, 1, 8, generator=g)
+    a2[0, 0, 0] = 0.0
+    got = pa.merge_partials((m1, l1, a1), (m2, l2, a2))
+    ref = orc.merge_states((m1, l1, a1), (m2, l2, a2))
+    for x, y in zip(got, ref):
+        assert torch.equal(x, y)
+    both_empty = pa.merge_partials((m2[:1, :1], l2[:1, :1], a2[:1, :1]), (m2[:1, :1], l2[:1, :1], a2[:1, :1]))
+    assert float(both_empty[1].abs().max()) == 0.0 and not torch.isnan(both_empty[2]).any()
+    Pi = orc.rotation_matrix(8, 7)
+    x = torch.randn(4, 8, generator=g)
+    assert torch.equal(pa.rotate_query(x, Pi), x @ Pi.T)
+    assert torch.equal(pa.rotate_output(x, Pi), x @ Pi)
+    assert torch.allclose(pa.rotate_output(pa.rotate_query(x, Pi), Pi), x, atol=1e-5)
+
+
+def test_operators_refuse_cpu_tensors():
+    """There is no CPU implementation behind the reference's operator names."""
+    import pytest
+    import torch
+    import cases
+    from helpers import oracle_case
+    from winnow_b200 import packed_attention as pa
+    c = next(x for x in cases.ATTENTION_CASES if x.name == "val_tail")
+    q, okv, _ = oracle_case(c)
+    kv = pa.PackedKV(okv.k_pages, okv.k_norms, okv.v_pages, okv.v_norms, okv.page_table,
+                     okv.seq_lens, pa.Quantizer(okv.k_Pi, okv.k_centroids, okv.k_bits),
+                     pa.Quantizer(okv.v_Pi, okv.v_centroids, okv.v_bits), c.D)
+    for fn in (pa.tiled_compressed_attention, pa.explicit_compressed_attention,
+               pa.reconstruct_attention):
+        with pytest.raises(pa.UnsupportedLayout):
+            fn(q, kv, 0.1)

@@ -158,6 +158,123 @@ def default_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(head_dim)
 
 
+def rotate_query(q: torch.Tensor, Pi: torch.Tensor) -> torch.Tensor:
+    """Row vector q into the quantizer basis: q Pi^T
+    (reference: turboquant_kv/packed_attention.py:173-175)."""
+    return q @ Pi.T
+
+
+def rotate_output(a_rot: torch.Tensor, Pi: torch.Tensor) -> torch.Tensor:
+    """Row vector in the quantizer basis back to the model basis: a Pi
+    (reference: turboquant_kv/packed_attention.py:178-180)."""
+    return a_rot @ Pi
+
+
+def _safe_exp(x: torch.Tensor, m: torch.Tensor) -> torch.Tensor:
+    """exp(x - m) with exp(-inf - -inf) defined as 0."""
+    return torch.where(torch.isneginf(m) | torch.isneginf(x), torch.zeros_like(x), torch.exp(x - m))
+
+
+def merge_partials(left, right):
+    """Combine two online-softmax states (m, l, a) covering disjoint key ranges
+    (reference: turboquant_kv/packed_attention.py:328-334)."""
+    m1, l1, a1 = left
+    m2, l2, a2 = right
+    m = torch.maximum(m1, m2)
+    w1, w2 = _safe_exp(m1, m), _safe_exp(m2, m)
+    return m, w1 * l1 + w2 * l2, w1[..., None] * a1 + w2[..., None] * a2
+
+
+def _require_cuda(q: torch.Tensor, what: str) -> None:
+    if not q.is_cuda:
+        raise UnsupportedLayout(f"{what}: this package has no CPU implementation; "
+                                "operands must be CUDA tensors")
+
+
+def _causal_rows(q: torch.Tensor, kv: PackedKV):
+    """A chunk of Q query tokens as B * Q one-token sequences over the same
+    pages: query i of sequence b sits at position seq_lens[b] - Q + i (the
+    cache already holds the chunk) and sees the seq_lens[b] - (Q - 1 - i) keys
+    up to itself (reference: `_causal_limit`,
+    turboquant_kv/packed_attention.py:203-211)."""
+    B, Hq, Q, D = q.shape
+    rows = q.permute(0, 2, 1, 3).reshape(B * Q, Hq, 1, D)
+    if Q == 1:
+        return rows, kv
+    back = torch.arange(Q - 1, -1, -1, device=kv.seq_lens.device, dtype=torch.int32)
+    lens = (kv.seq_lens[:, None] - back[None, :]).clamp_(min=0).reshape(B * Q).contiguous()
+    table = kv.page_table.repeat_interleave(Q, dim=0).contiguous()
+    return rows, PackedKV(kv.k_pages, kv.k_norms, kv.v_pages, kv.v_norms, table, lens,
+                          kv.k_quant, kv.v_quant, kv.head_dim)
+
+
+def tiled_compressed_attention(q: torch.Tensor, kv: PackedKV, scale: float,
+                               split_pages: int | None = None) -> torch.Tensor:
+    """Causal attention of (B, Hq, Q, D) queries over the packed pages, fp32
+    result, on the split-K page-scan kernels: the schedule of the reference's
+    operator of this name (turboquant_kv/packed_attention.py:260-311: online
+    softmax in the quantizer bases, one rotation of q and one of the output,
+    rows that see no key return exact zeros) run on the GPU.  A chunk of Q > 1
+    query tokens is one launch over B * Q rows that share the pages, each with
+    its own causal length: prefill over packed pages without reconstructing the
+    history.  `split_pages` (pages per split, as in the reference) fixes the
+    split-K factor; None lets the backend choose."""
+    check_contract(q, kv)
+    _require_cuda(q, "tiled_compressed_attention")
+    from .packed_attention_cuda import packed_decode_attention
+    B, Hq, Q, D = q.shape
+    rows, view = _causal_rows(q.float(), kv)
+    splits = None if not split_pages else max(1, -(-kv.page_table.shape[1] // int(split_pages)))
+    out = packed_decode_attention(rows.contiguous(), view, scale, num_splits=splits,
+                                  check_page_ids=False)
+    return out.view(B, Q, Hq, D).permute(0, 2, 1, 3).contiguous()
+
+
+def explicit_compressed_attention(q: torch.Tensor, kv: PackedKV, scale: float) -> torch.Tensor:
+    """The reference's single-softmax form of the same algebra
+    (turboquant_kv/packed_attention.py:238-257).  On the GPU there is one
+    schedule for it: this is `tiled_compressed_attention` with one split."""
+    return tiled_compressed_attention(q, kv, scale, split_pages=kv.page_table.shape[1])
+
+
+def reconstruct_attention(q: torch.Tensor, kv: PackedKV, scale: float) -> torch.Tensor:
+    """Dequantize every sequence's history (fused unpack, gather, rotate and
+    scale kernel), then plain causal attention in fp32 on the same device: the
+    independent check of the compressed-domain operators
+    (reference: turboquant_kv/packed_attention.py:214-235)."""
+    check_contract(q, kv)
+    _require_cuda(q, "reconstruct_attention")
+    from .cache import dequantize_rows
+    B, Hq, Q, D = q.shape
+    S = kv.page_size
+    n_rep = Hq // kv.num_kv_heads
+    out = torch.zeros(B, Hq, Q, D, dtype=torch.float32, device=q.device)
+    lens = kv.seq_lens.tolist()
+    heads = kv_head_for(torch.arange(Hq, device=q.device), n_rep)
+    pos = torch.arange(Q, device=q.device)
+    for b, L in enumerate(lens):
+        if L <= 0:
+            continue
+        ids = kv.page_table[b, :(L + S - 1) // S].long()
+        sides = []
+        for pages, norms, quant in ((kv.k_pages, kv.k_norms, kv.k_quant),
+                                    (kv.v_pages, kv.v_norms, kv.v_quant)):
+            rows = pages[ids].permute(1, 0, 2, 3).reshape(pages.shape[1], -1, pages.shape[3])[:, :L]
+            nrm = norms[ids].permute(1, 0, 2).reshape(norms.shape[1], -1)[:, :L]
+            rows = rows.contiguous()
+            full = torch.empty(*rows.shape[:-1], D, dtype=torch.float32, device=q.device)
+            sides.append(dequantize_rows(rows, nrm.contiguous(), quant.centroids, quant.Pi,
+                                         quant.bit_width, D, out=full)[heads])
+        k, v = sides                                                  # (Hq, L, D)
+        s = (q[b].float() @ k.transpose(-1, -2)) * scale             # (Hq, Q, L)
+        limit = L - Q + pos                                           # last key query i may see
+        allowed = torch.arange(L, device=q.device)[None, :] <= limit[:, None]
+        s = s.masked_fill(~allowed[None], float("-inf"))
+        p = torch.softmax(s, dim=-1).nan_to_num(0.0)
+        out[b] = (p @ v) * allowed.any(-1)[None, :, None]
+    return out
+
+
 @torch.no_grad()
 def pages_from_dense(k: torch.Tensor, v: torch.Tensor, seq_lens, k_tq, v_tq, page_size: int,
                      num_pages: int | None = None,
