@@ -191,6 +191,11 @@ def test_attention_interface_entry_point():
     assert pb.BACKEND_COUNTS["prefill_reconstruct_sdpa"] == 1
     ref5 = orc.reconstruct_attention(q5, okv, 0.09)
     assert (out5.transpose(1, 2).cpu() - ref5).abs().max() < 2e-3
+    kv.prefill_backend = "packed"        # additive: the chunk on the page-scan kernels
+    out5p, _ = pb.winnow_packed_attention(None, q5.to(DEV), kv, kv, None, scaling=0.09)
+    assert pb.BACKEND_COUNTS["prefill_cuda_packed"] == 1
+    assert out5p.shape == out5.shape and out5p.dtype == out5.dtype
+    assert (out5p.transpose(1, 2).cpu() - ref5).abs().max() < 2e-3
 
 
 def test_append_then_decode_through_the_cache():

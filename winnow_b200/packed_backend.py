@@ -102,7 +102,13 @@ class PagedPackedCache:
     """
 
     def __init__(self, pool: PagePool, owners, lengths, *, k_quant, v_quant, head_dim: int,
-                 decode_backend: str = "auto"):
+                 decode_backend: str = "auto", prefill_backend: str = "reconstruct"):
+        """`prefill_backend`: "reconstruct" (the reference's path: dequantize the
+        history, stock attention) or "packed" (additive: the chunk's queries run
+        on the page-scan kernels as one causal launch, no reconstruction)."""
+        if prefill_backend not in ("reconstruct", "packed"):
+            raise ValueError(f"unknown prefill_backend {prefill_backend!r}")
+        self.prefill_backend = prefill_backend
         self.pool = pool
         self.owners = list(owners)
         self.lengths = list(lengths)
@@ -166,6 +172,7 @@ class PagedPackedCache:
                                  pa.Quantizer.from_tq(self.vq), D)
             handle.table_validated = True      # ids come from validated page refs
         handle.decode_backend = self.decode_backend
+        handle.prefill_backend = self.prefill_backend
         if last:
             self.lengths = [L + n for L in self.lengths]
         return handle, handle
@@ -324,6 +331,9 @@ def winnow_packed_attention(module, query, key, value, attention_mask, dropout: 
         backend = "dense_sdpa" if Q > 1 else select_decode_backend(query, key, requested)
         BACKEND_COUNTS[("prefill_" if Q > 1 else "") + backend] += 1
         out = _dense_sdpa(query, key, scaling)
+    elif Q > 1 and getattr(key, "prefill_backend", "reconstruct") == "packed" and query.is_cuda:
+        BACKEND_COUNTS["prefill_cuda_packed"] += 1
+        out = pa.tiled_compressed_attention(query, key, scaling).to(query.dtype)
     elif Q > 1:
         BACKEND_COUNTS["prefill_reconstruct_sdpa"] += 1
         out = _reconstruct_sdpa(query, key, scaling)
