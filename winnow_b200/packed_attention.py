@@ -209,7 +209,8 @@ def _causal_rows(q: torch.Tensor, kv: PackedKV):
 
 
 def tiled_compressed_attention(q: torch.Tensor, kv: PackedKV, scale: float,
-                               split_pages: int | None = None) -> torch.Tensor:
+                               split_pages: int | None = None, *,
+                               check_page_ids: bool = True) -> torch.Tensor:
     """Causal attention of (B, Hq, Q, D) queries over the packed pages, fp32
     result, on the split-K page-scan kernels: the schedule of the reference's
     operator of this name (turboquant_kv/packed_attention.py:260-311: online
@@ -218,8 +219,10 @@ def tiled_compressed_attention(q: torch.Tensor, kv: PackedKV, scale: float,
     query tokens is one launch over B * Q rows that share the pages, each with
     its own causal length: prefill over packed pages without reconstructing the
     history.  `split_pages` (pages per split, as in the reference) fixes the
-    split-K factor; None lets the backend choose."""
-    check_contract(q, kv)
+    split-K factor; None lets the backend choose.  `check_page_ids=False`
+    (additive) skips the host-side check of lengths and page ids, which waits
+    for the stream, when the table comes from validated page references."""
+    check_contract(q, kv, check_page_ids=check_page_ids)
     _require_cuda(q, "tiled_compressed_attention")
     from .packed_attention_cuda import packed_decode_attention
     B, Hq, Q, D = q.shape

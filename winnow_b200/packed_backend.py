@@ -333,7 +333,9 @@ def winnow_packed_attention(module, query, key, value, attention_mask, dropout: 
         out = _dense_sdpa(query, key, scaling)
     elif Q > 1 and getattr(key, "prefill_backend", "reconstruct") == "packed" and query.is_cuda:
         BACKEND_COUNTS["prefill_cuda_packed"] += 1
-        out = pa.tiled_compressed_attention(query, key, scaling).to(query.dtype)
+        out = pa.tiled_compressed_attention(
+            query, key, scaling,
+            check_page_ids=not getattr(key, "table_validated", False)).to(query.dtype)
     elif Q > 1:
         BACKEND_COUNTS["prefill_reconstruct_sdpa"] += 1
         out = _reconstruct_sdpa(query, key, scaling)
