@@ -58,3 +58,33 @@ def test_argument_errors_are_reported_without_a_gpu(library):
     small = library.wtq_decode_workspace_bytes(2, 8, 2, 128, 4, 16, 1)
     big = library.wtq_decode_workspace_bytes(2, 8, 2, 128, 4096, 16, 8)
     assert 0 < small < big
+
+
+def test_auto_splits_fills_the_last_round_of_worker_warps():
+    """`wtq_decode_auto_splits` is host arithmetic (148 SMs assumed without a
+    GPU): for the tensor-core shapes it picks the chunk, a multiple of 32 tokens
+    in [64, 512], whose items just fill a whole number of rounds of the 2368
+    worker warps; the answers for the benchmark shapes are pinned."""
+    from winnow_b200 import _lib
+    f = _lib.lib().wtq_decode_auto_splits
+    workers = 148 * 16
+
+    def items(B, Hkv, ctx, S, bk, bv, n_rep=4):
+        splits = f(B, Hkv * n_rep, Hkv, 128, -(-ctx // S), S, bk, bv)
+        assert 1 <= splits <= 1024
+        chunk = -(-(-(-ctx // splits)) // 32) * 32
+        assert 64 <= chunk <= 512 or ctx <= 64
+        return splits, B * Hkv * -(-ctx // chunk)
+
+    assert items(16, 8, 8192, 16, 4, 4) == (18, 2304)           # config 2: one round
+    assert items(16, 4, 8192, 16, 4, 4) == (37, 2368)           # its 2-GPU shard: exactly one round
+    assert items(16, 1, 8192, 16, 4, 4)[0] == 128               # its 8-GPU shard: 64-token chunks
+    assert items(16, 8, 32768, 16, 4, 4) == (74, 4 * workers)   # 32k context: four full rounds
+    assert items(1, 8, 131072, 64, 4, 4, n_rep=8)[0] == 293     # config 4
+    assert items(128, 8, 32768, 16, 4, 6)[0] == 64              # config 5: 512-token chunks
+    # degenerate sizes stay in range
+    assert f(1, 4, 1, 128, 1, 16, 4, 4) >= 1
+    assert f(0, 4, 1, 128, 1, 16, 4, 4) == 1
+    assert 1 <= f(1, 8, 1, 128, 1 << 20, 16, 4, 4) <= 1024
+    # shapes without a tensor-core kernel use the generic rule and stay in range
+    assert 1 <= f(4, 8, 2, 64, 64, 16, 8, 8) <= 1024
