@@ -700,6 +700,7 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
     MergeParams p, const int32_t *seq_lens, int num_groups, int Hkv, int n_rep, int hpb,
     int chunk_tokens, int max_tokens) {
   __shared__ float a_s[8][128];           // [way * hpb + head][coordinate] partial chunk sums
+  __shared__ __align__(16) float at_s[128][8];   // [coordinate][head] normalised sums, for the rotation
   __shared__ float w_s[8][kMaxSplits];    // chunk weights; reused for the rotation's partial sums
   __shared__ float inv_s[8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -837,24 +838,36 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
     const int h = e >> 7, d = e & 127;
     float a = a_s[h][d];
     for (int w = 1; w < ways; ++w) a += a_s[w * hpb + h][d];
-    a_s[h][d] = a * inv_s[h];
+    at_s[d][h] = a * inv_s[h];
   }
   __syncthreads();
   if (group + (int)gridDim.x < num_groups) preload(group + gridDim.x);   // next group's states
   float o[8];
 #pragma unroll
   for (int h = 0; h < 8; ++h) o[h] = 0.f;
+  // (heads hpb .. 7 of at_s are never written and the sums made of them are
+  // never stored; a group of at most four heads skips the second half)
+  const bool wide = hpb > 4;
 #pragma unroll
-  for (int i = 0; i < 32; ++i)
-#pragma unroll
-    for (int h = 0; h < 8; ++h)
-      o[h] = fmaf(h < hpb ? a_s[h][part * 32 + i] : 0.f, pi_s[(part * 32 + i) * 128 + col], o[h]);
+  for (int i = 0; i < 32; ++i) {
+    const int d = part * 32 + i;
+    const float w = pi_s[d * 128 + col];
+    const float4 x = *reinterpret_cast<const float4 *>(&at_s[d][0]);
+    o[0] = fmaf(x.x, w, o[0]); o[1] = fmaf(x.y, w, o[1]);
+    o[2] = fmaf(x.z, w, o[2]); o[3] = fmaf(x.w, w, o[3]);
+    if (wide) {
+      const float4 y = *reinterpret_cast<const float4 *>(&at_s[d][4]);
+      o[4] = fmaf(y.x, w, o[4]); o[5] = fmaf(y.y, w, o[5]);
+      o[6] = fmaf(y.z, w, o[6]); o[7] = fmaf(y.w, w, o[7]);
+    }
+  }
   // the weights are consumed (second barrier above): their storage now holds the
   // partial outputs of quarters 1..3; quarter 0 stays in registers
   float (*o_s)[8][128] = reinterpret_cast<float (*)[8][128]>(&w_s[0][0]);
   if (part > 0) {
 #pragma unroll
-    for (int h = 0; h < 8; ++h) o_s[part][h][col] = o[h];
+    for (int h = 0; h < 8; ++h)
+      if (h < hpb) o_s[part][h][col] = o[h];
   }
   __syncthreads();
   if (part == 0) {
