@@ -262,6 +262,132 @@ __global__ void append_kernel(AppendParams p) {
   }
 }
 
+// A decode step's append at head_dim 128: NV vectors per block, so that the one
+// pass a thread makes over its row of Pi (32 16-byte loads) serves NV FMA
+// chains.  A block per vector makes the step L2-bound (64 KB of Pi per
+// vector); sharing the pass divides that traffic by NV.  Same arithmetic, in
+// the same order, as quantize_vector with WTQ_ORDER_SEQUENTIAL.
+template <int NV>
+__global__ void __launch_bounds__(128) append_multi_kernel(AppendParams p) {
+  __shared__ float x_s[NV][128];
+  __shared__ float lane_s[NV][8];
+  __shared__ float norm_s[NV];
+  __shared__ float bounds_s[255];
+  __shared__ uint8_t idx_s[NV][128];
+  __shared__ int64_t dest_s[NV][2];
+  const AppendSideDev &a = p.side[blockIdx.y];
+  const int c = threadIdx.x;
+  for (int e = c; e < a.q.nbounds; e += 128) bounds_s[e] = a.q.bounds[e];
+  const int64_t vectors = (int64_t)p.B * p.Hkv * p.n;
+  const float4 *row = reinterpret_cast<const float4 *>(a.q.Pi + (int64_t)c * 128);
+  for (int64_t v0 = (int64_t)blockIdx.x * NV; v0 < vectors; v0 += (int64_t)gridDim.x * NV) {
+    // the first half of the thread's row of Pi is requested before anything
+    // else: its trip to L2 overlaps the loads and barriers of the normalisation
+    float4 wa[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) wa[k] = __ldg(row + k);
+    if (c < NV) {
+      // Where the token goes; -1 marks a position or page the table does not
+      // cover (reported through `status`, not written) or a vector past the end.
+      const int64_t vec = v0 + c;
+      int64_t code_off = -1, norm_off = -1;
+      if (vec < vectors) {
+        const int i = (int)(vec % p.n);
+        const int h = (int)((vec / p.n) % p.Hkv);
+        const int b = (int)(vec / ((int64_t)p.n * p.Hkv));
+        const int pos = p.seq_lens[b] - p.n + i;
+        const int slot_page = pos >= 0 ? pos / p.S : -1;
+        if (pos < 0 || slot_page >= p.max_pages) {
+          if (p.status) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+        } else {
+          const int pid = p.page_table[(int64_t)b * p.table_stride + slot_page];
+          if (pid < 0 || pid >= p.P) {
+            if (p.status) atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+          } else {
+            const int slot = pos - slot_page * p.S;
+            code_off = (int64_t)pid * a.page_stride + (int64_t)h * a.head_stride +
+                       (int64_t)slot * a.q.nb;
+            norm_off = (int64_t)pid * a.norm_page_stride + (int64_t)h * a.norm_head_stride + slot;
+          }
+        }
+      }
+      dest_s[c][0] = code_off;
+      dest_s[c][1] = norm_off;
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int64_t vec = v0 + j;
+      float v = 0.0f;
+      if (vec < vectors) {
+        const int i = (int)(vec % p.n);
+        const int h = (int)((vec / p.n) % p.Hkv);
+        const int b = (int)(vec / ((int64_t)p.n * p.Hkv));
+        v = load_as_float(a.src, (int64_t)b * a.sb + (int64_t)h * a.sh + (int64_t)i * a.st + c,
+                          p.dtype);
+      }
+      x_s[j][c] = v;
+    }
+    __syncthreads();
+    if (c < 8 * NV) {
+      const int j = c >> 3, l = c & 7;
+      float acc = 0.0f;
+      for (int d = l; d < 128; d += 8) acc = __fadd_rn(acc, __fmul_rn(x_s[j][d], x_s[j][d]));
+      lane_s[j][l] = acc;
+    }
+    __syncthreads();
+    if (c < NV) {
+      float t = lane_s[c][0];
+#pragma unroll
+      for (int l = 1; l < 8; ++l) t = __fadd_rn(t, lane_s[c][l]);
+      norm_s[c] = fmaxf(__fsqrt_rn(t), 1e-10f);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < NV; ++j) x_s[j][c] = __fdiv_rn(x_s[j][c], norm_s[j]);
+    __syncthreads();
+    float acc[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) acc[j] = 0.0f;
+    float4 wb[16];                                         // second half, while the first is used
+#pragma unroll
+    for (int k = 0; k < 16; ++k) wb[k] = __ldg(row + 16 + k);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float4 w = half ? wb[k] : wa[k];
+        const int d = 64 * half + 4 * k;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          acc[j] = __fmaf_rn(x_s[j][d + 0], w.x, acc[j]);
+          acc[j] = __fmaf_rn(x_s[j][d + 1], w.y, acc[j]);
+          acc[j] = __fmaf_rn(x_s[j][d + 2], w.z, acc[j]);
+          acc[j] = __fmaf_rn(x_s[j][d + 3], w.w, acc[j]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      int lo = 0, hi = a.q.nbounds;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (bounds_s[mid] < acc[j]) lo = mid + 1;
+        else hi = mid;
+      }
+      idx_s[j][c] = (uint8_t)lo;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (dest_s[j][0] >= 0) {
+        if (c < a.q.nb) a.pages[dest_s[j][0] + c] = packed_byte(idx_s[j], c, a.q.bw);
+        if (c == 0) a.norms[dest_s[j][1]] = __float2half_rn(norm_s[j]);
+      }
+    }
+    __syncthreads();
+  }
+}
+
 static int block_threads(int D) { return ((D + 31) / 32) * 32; }
 
 template <typename K, typename P>
@@ -349,6 +475,15 @@ extern "C" int wtq_append(const void *k, const void *v, int dtype, const int64_t
   p.page_table = page_table; p.table_stride = table_stride; p.seq_lens = seq_lens;
   p.dtype = dtype; p.B = B; p.Hkv = Hkv; p.n = n; p.D = D; p.S = S; p.P = P;
   p.max_pages = max_pages; p.order = resolve_order(order, vectors); p.status = status;
+  // decode-step sizes at head_dim 128: four vectors share a block's pass over Pi
+  constexpr int kMultiVectors = 4;
+  if (D == 128 && p.order == WTQ_ORDER_SEQUENTIAL && vectors >= 2 * kMultiVectors &&
+      vectors <= 4 * 3 * 148 && p.side[0].q.vec4 && p.side[1].q.vec4) {
+    dim3 grid((unsigned)((vectors + kMultiVectors - 1) / kMultiVectors), 2);
+    append_multi_kernel<kMultiVectors><<<grid, 128, 0, (cudaStream_t)stream>>>(p);
+    note_launches(1);
+    return check_cuda(cudaGetLastError(), "wtq_append launch");
+  }
   return launch_staged(append_kernel<true>, append_kernel<false>, p, D, vectors, 2,
                        (cudaStream_t)stream, "wtq_append launch");
 }
