@@ -48,6 +48,9 @@ extern "C" {
 /* status bits written by kernels */
 #define WTQ_STATUS_BAD_PAGE 1     /* page id outside [0, P) was skipped */
 #define WTQ_STATUS_BAD_POSITION 2 /* token position outside the page table */
+/* (4 is WTQ_STATUS_EXCHANGE_TIMEOUT, below) */
+#define WTQ_STATUS_LAYOUT 8        /* the scan kernel found its shared-memory plan unusable and did nothing */
+#define WTQ_STATUS_SCAN_TIMEOUT 16 /* a page copy of the scan kernel did not complete within its bounded wait */
 
 /* order of the fp32 summation in the rotation of wtq_quantize / wtq_append.
  * The reference computes (x/|x|) @ Pi^T with a CPU BLAS whose order depends

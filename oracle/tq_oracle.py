@@ -376,8 +376,14 @@ def merge_states(a, b):
 
 
 def tiled_attention(q: torch.Tensor, kv: OracleKV, scale: float,
-                    split_pages: int | None = None) -> torch.Tensor:
+                    split_pages: int | None = None, mutant: str | None = None) -> torch.Tensor:
     """Compressed-domain attention, one page slot at a time, online softmax.
+
+    `mutant` plants one of the reference suite's schedule mistakes
+    (turboquant_kv/test_packed_attention.py:246-264) for detection-power tests:
+    "update_without_rescale" keeps the old state unscaled when the running
+    maximum moves, "merge_without_rescale" adds split states as if they shared
+    one maximum.
 
     q is rotated into the key basis once (q Pi_K^T, times scale); each page
     contributes scores n_K (q_rot . c_K) and values p n_V c_V accumulated in
@@ -412,6 +418,8 @@ def tiled_attention(q: torch.Tensor, kv: OracleKV, scale: float,
             s = s.masked_fill(hidden[:, None], float("-inf"))
             m_new = torch.maximum(m, s.amax(-1))
             alpha = torch.where(torch.isneginf(m), torch.zeros_like(m), torch.exp(m - m_new))
+            if mutant == "update_without_rescale":
+                alpha = torch.ones_like(alpha)
             p = torch.where(torch.isneginf(s), torch.zeros_like(s), torch.exp(s - m_new[..., None]))
             l = alpha * l + p.sum(-1)
             acc = alpha[..., None] * acc + (p * nv[:, :, None, :]) @ cv
@@ -419,7 +427,10 @@ def tiled_attention(q: torch.Tensor, kv: OracleKV, scale: float,
         states.append((m, l, acc))
     m, l, acc = states[0]
     for st in states[1:]:
-        m, l, acc = merge_states((m, l, acc), st)
+        if mutant == "merge_without_rescale":
+            m, l, acc = torch.maximum(m, st[0]), l + st[1], acc + st[2]
+        else:
+            m, l, acc = merge_states((m, l, acc), st)
     a = torch.where(l[..., None] > 0, acc / l.clamp(min=1e-30)[..., None], torch.zeros(()))
     return a @ kv.v_Pi
 

@@ -39,8 +39,7 @@ def test_decode_matches_reference(golden, c, splits, kernel_path):
     got = packed_decode_attention(q.to(DEV), to_device(okv, DEV), orc.default_scale(c.D),
                                   num_splits=splits)
     assert got.shape == q.shape and got.dtype == q.dtype
-    tol = ATOL * max(1.0, float(ref.abs().max()))
-    assert_attention_close(got, ref, atol=tol)
+    assert_attention_close(got, ref)        # plain bounds: 2e-3 max-abs, 1e-3 relative L2
     for b, L in enumerate(c.lens):
         if L == 0:
             assert (got[b] == 0).all()
@@ -413,3 +412,104 @@ def test_reference_operator_names_on_the_gpu(name, Q):
             for i in range(Q):
                 if L - (Q - 1 - i) <= 0:
                     assert float(got[b, :, i].abs().max()) == 0.0
+
+
+def test_exchange_wait_gives_up_and_says_so():
+    """The bounded wait of the output exchange, made to run out on purpose: the
+    flags are one step behind (nothing will ever set them), the poll limit is
+    small, so the kernel must return, set WTQ_STATUS_EXCHANGE_TIMEOUT and leave
+    the device usable; with the flags set a second wait reports nothing."""
+    lib = _lib.lib()
+    dev = torch.device("cuda", 0)
+    world = 2
+    flags = torch.zeros(world, dtype=torch.int32, device=dev)
+    step = torch.ones(1, dtype=torch.int32, device=dev)          # the step being waited for
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 8,
+                                     status.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert int(status.item()) & _lib.STATUS_EXCHANGE_TIMEOUT
+    # one rank arrived, the other did not: still a timeout
+    status.zero_()
+    flags[0] = 1
+    _lib.check(lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 8,
+                                     status.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert int(status.item()) & _lib.STATUS_EXCHANGE_TIMEOUT
+    # everybody arrived: nothing to report, and the context still works
+    status.zero_()
+    flags.fill_(1)
+    _lib.check(lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 8,
+                                     status.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert float((torch.ones(4, device=dev) * 2).sum().item()) == 8.0
+    # malformed calls are refused before any launch
+    assert lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 0, status.data_ptr(),
+                                 stream) != 0
+    assert lib.wtq_exchange_wait(None, world, step.data_ptr(), 8, status.data_ptr(), stream) != 0
+
+
+# Seeded wrong implementations of the operator (the reference keeps the same
+# list for its own suite, turboquant_kv/test_packed_attention.py:207-264): each
+# is applied to the CPU oracle and must land at least 100 x ATOL away from what
+# the GPU computes, i.e. the parity bound used throughout this file would
+# notice that specific mistake if the kernels made it.
+def _mutant_outputs(q, okv, scale):
+    import copy
+    D = okv.head_dim
+    out = {}
+
+    def run(kv=okv, qq=q, sc=scale, **kw):
+        return orc.tiled_attention(qq, kv, sc, **kw)
+
+    swapped = copy.copy(okv)                                   # q rotated with Pi instead of Pi^T
+    swapped.k_Pi = okv.k_Pi.t().contiguous()
+    out["transposed_query_rotation"] = run(kv=swapped)
+    swapped = copy.copy(okv)                                   # output rotated with Pi^T
+    swapped.v_Pi = okv.v_Pi.t().contiguous()
+    out["transposed_output_rotation"] = run(kv=swapped)
+    out["missing_scale"] = run(sc=1.0)
+    wrong_basis = copy.copy(okv)                               # V decoded in the K basis
+    wrong_basis.v_Pi = okv.k_Pi
+    out["values_in_key_basis"] = run(kv=wrong_basis)
+    Hq, Hkv = q.shape[1], okv.k_pages.shape[1]
+    n_rep = Hq // Hkv
+    if n_rep > 1 and Hkv > 1:                                  # h % Hkv head map instead of h // n_rep
+        # head h must end up reading kv head h % Hkv: feed it to the oracle as head
+        # (h % Hkv) * n_rep + h // Hkv, whose kv head under the right map is h % Hkv
+        perm = torch.tensor([(h % Hkv) * n_rep + h // Hkv for h in range(Hq)])
+        out["modulo_head_map"] = run(qq=q[:, torch.argsort(perm)])[:, perm]
+    return out
+
+
+@pytest.mark.parametrize("name", ["qwen7b_gqa_mixed", "gqa8_2", "val_long"])
+def test_seeded_mutants_of_the_oracle_miss_the_gpu_output(name):
+    c = next(x for x in cases.ATTENTION_CASES if x.name == name)
+    q, okv, _ = oracle_case(c)
+    scale = orc.default_scale(c.D)
+    got = packed_decode_attention(q.to(DEV), to_device(okv, DEV), scale).float().cpu()
+    assert_attention_close(got, orc.tiled_attention(q, okv, scale))
+    mutants = _mutant_outputs(q, okv, scale)
+    assert len(mutants) >= 4
+    for label, wrong in mutants.items():
+        miss = float((wrong - got).abs().max())
+        assert miss >= 100 * ATOL, f"mutant {label} is only {miss:.3e} away from the GPU output"
+
+
+@pytest.mark.parametrize("name", ["huge_scores", "val_huge"])
+def test_online_softmax_mutants_miss_the_gpu_output(name):
+    """The two schedule mutants of the reference's list, planted in the oracle:
+    an online softmax that forgets to rescale its state when the maximum moves,
+    and a split merge that adds chunk states without their weights.  Run on the
+    cases whose scores are large enough for the maximum to move a lot."""
+    c = next(x for x in cases.ATTENTION_CASES if x.name == name)
+    q, okv, _ = oracle_case(c)
+    scale = orc.default_scale(c.D)
+    got = packed_decode_attention(q.to(DEV), to_device(okv, DEV), scale).float().cpu()
+    assert_attention_close(got, orc.tiled_attention(q, okv, scale))
+    for label, kwargs in (("update_without_rescale", {}), ("merge_without_rescale", {"split_pages": 1})):
+        wrong = orc.tiled_attention(q, okv, scale, mutant=label, **kwargs)
+        miss = float((wrong - got).abs().max())
+        assert miss >= 100 * ATOL, f"mutant {label} is only {miss:.3e} away from the GPU output"

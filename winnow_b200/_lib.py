@@ -3,6 +3,7 @@ absent or a call fails, the caller gets an exception."""
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
 
 import torch
@@ -87,11 +88,12 @@ def exported_symbols() -> list[str]:
 def lib():
     global _lib
     if _lib is None:
-        if not LIB.exists():
+        path = os.environ.get("WTQ_LIB_PATH", str(LIB))   # development aid: an alternative build
+        if not os.path.exists(path):
             raise BackendError(
                 f"{LIB} is not built; run `python -c \"import __graft_entry__ as g; g.build()\"` "
                 "(needs nvcc). This package has no CPU or library fallback.")
-        handle = ctypes.CDLL(str(LIB))
+        handle = ctypes.CDLL(path)
         for name, (res, args) in _SIGNATURES.items():
             fn = getattr(handle, name)     # AttributeError if the symbol is missing
             fn.restype, fn.argtypes = res, args

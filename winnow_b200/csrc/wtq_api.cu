@@ -10,6 +10,9 @@ namespace {
 
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// lookup tables of the tensor-core scan: at most 256 entries x 2 sides x 32 lanes
+constexpr size_t kLutBytesMax = 256 * 256;
+
 int device_sms() {
   static int sms = 0;
   if (sms == 0) {
@@ -76,12 +79,12 @@ extern "C" int wtq_decode_auto_splits(int B, int Hq, int Hkv, int D, int max_pag
     // throughput, so a part-filled last round costs less than a full one but
     // is not free.  Measured on B200, the best chunk is the one that fills
     // the last round (items just under a multiple of the workers); the search
-    // below finds it.  Lengths are taken at the table's full width.  A chunk
-    // above 512 tokens leaves one warp running long after the others.
+    // below finds it.  Lengths are taken at the table's full width.  Chunks are
+    // capped at 1024 tokens: beyond that one warp runs long after the others.
     const int64_t workers = (int64_t)device_sms() * warps;
     int64_t lo = ((max_tokens + kMaxSplits - 1) / kMaxSplits + 31) / 32 * 32;
     if (lo < 64) lo = 64;
-    int64_t hi = lo > 512 ? lo : 512;
+    int64_t hi = lo > 1024 ? lo : 1024;
     int64_t best = hi;
     double best_cost = 0;
     for (int64_t chunk = hi; chunk >= lo; chunk -= 32) {
@@ -106,6 +109,7 @@ static size_t workspace_for(int B, int Hq, int Hkv, int D, int splits) {
   bytes += round_up(rows * D * sizeof(float), 256);                   // rotated query
   bytes += round_up(rows * splits * D * sizeof(float), 256);          // partial acc
   bytes += 2 * round_up(rows * splits * sizeof(float), 256);          // partial m, l
+  bytes += kLutBytesMax;                                              // lookup tables of the scan
   return bytes;
 }
 
@@ -172,6 +176,8 @@ static int decode_common(const void *q, int dtype, const int64_t q_strides[2], v
   p.part_m = (float *)ws;
   ws += round_up(rows * splits * sizeof(float), 256);
   p.part_l = (float *)ws;
+  ws += round_up(rows * splits * sizeof(float), 256);
+  p.lut = (const uint32_t *)ws;
 
   p.q_rot = q_rot;
   p.page_table = page_table;
@@ -206,9 +212,17 @@ static int decode_common(const void *q, int dtype, const int64_t q_strides[2], v
   const int max_tokens = max_pages * S;
   m.work_counter = fast ? p.work_counter : nullptr;
   profile_mark_call(stream, true);
+  ScanSetup setup = {nullptr, nullptr, nullptr, nullptr, 0, 0, 0};
+  if (fast) {
+    setup.chunk_prefix = chunk_prefix;
+    setup.lut = (uint32_t *)p.lut;
+    setup.cent_k = k_side->centroids; setup.cent_v = v_side->centroids;
+    setup.bw_k = k_side->bw; setup.bw_v = v_side->bw;
+    setup.lut_words = mma_lut_words(k_side->bw, v_side->bw);
+  }
   if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, q_scale, B, Hq, D, q_rot, seq_lens,
-                               fast ? mma_chunk_tokens(max_tokens, splits) : 1, max_tokens,
-                               fast ? chunk_prefix : nullptr, stream))
+                               fast ? mma_chunk_tokens(max_tokens, splits) : 1, max_tokens, setup,
+                               stream))
     return rc;
   int rc = 0;
   if (fast) {

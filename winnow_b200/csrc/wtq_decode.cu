@@ -43,6 +43,26 @@ __device__ void write_chunk_prefix(const int32_t *seq_lens, int B, int chunk_tok
   if (threadIdx.x == 0) chunk_prefix[B] = running;
 }
 
+// Side jobs of the rotation launch for the tensor-core scan: the last block's
+// first warp writes the chunk prefix; all blocks share the table words, each a
+// half2 of centroids: 4-bit tables are indexed by a packed byte ({c[lo nibble],
+// c[hi nibble]}), wider ones by a code ({c, c}); word = [index][key | value][lane].
+__device__ void scan_setup(const ScanSetup &s, const int32_t *seq_lens, int B, int chunk_tokens,
+                           int max_tokens) {
+  if (s.chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
+    write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, s.chunk_prefix);
+  if (s.lut == nullptr) return;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < s.lut_words; e += gridDim.x * blockDim.x) {
+    const int index = e >> 6, side = (e >> 5) & 1;
+    const int bw = side ? s.bw_v : s.bw_k;
+    const float *cent = side ? s.cent_v : s.cent_k;
+    __half2 h = __floats2half2_rn(0.f, 0.f);
+    if (bw == 4) h = __floats2half2_rn(__ldg(cent + (index & 15)), __ldg(cent + (index >> 4)));
+    else if (index < (1 << bw)) h = __floats2half2_rn(__ldg(cent + index), __ldg(cent + index));
+    s.lut[e] = *reinterpret_cast<uint32_t *>(&h);
+  }
+}
+
 // q_rot[row][c] = mult * sum_d q[row][d] Pi[c][d] for the `rows` query rows that
 // start at row blockIdx.x * NR.  A warp takes output coordinates c = warp,
 // warp + 16, ...; its lanes stride over d, so every Pi row is read once per
@@ -53,10 +73,9 @@ template <int NR>
 __global__ void __launch_bounds__(kRotThreads) rotate_q_kernel(
     const void *q, int dtype, int64_t qsb, int64_t qsh, const float *Pi, float mult, int Hq,
     int D, int total_rows, float *q_rot, const int32_t *seq_lens, int B, int chunk_tokens,
-    int max_tokens, int32_t *chunk_prefix) {
+    int max_tokens, ScanSetup setup) {
   __shared__ float qs[NR][256];
-  if (chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
-    write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, chunk_prefix);
+  scan_setup(setup, seq_lens, B, chunk_tokens, max_tokens);
   const int row0 = blockIdx.x * NR;
   for (int e = threadIdx.x; e < NR * D; e += kRotThreads) {
     const int r = e / D, d = e - r * D;
@@ -355,11 +374,10 @@ template <int NR>
 __global__ void __launch_bounds__(kRotThreads) rotate_q_rows_kernel(
     const void *q, int dtype, int64_t qsb, int64_t qsh, const float *Pi, float mult, int Hq,
     int D, int total_rows, float *q_rot, const int32_t *seq_lens, int B, int chunk_tokens,
-    int max_tokens, int32_t *chunk_prefix) {
+    int max_tokens, ScanSetup setup) {
   __shared__ __align__(16) float qs[256][NR];          // [coordinate][row]
   __shared__ float part_s[3][NR][256];
-  if (chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
-    write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, chunk_prefix);
+  scan_setup(setup, seq_lens, B, chunk_tokens, max_tokens);
   const int quarter = threadIdx.x >> 7, dq = D / 4, col = threadIdx.x & 127;
   // For head_dim <= 128 a thread's share of Pi (a quarter of one row, at most 8
   // float4) stays in registers for every group of rows this block processes.
@@ -435,11 +453,10 @@ template <int NR>
 __global__ void __launch_bounds__(kRotThreads) rotate_q128_kernel(
     const void *q, int dtype, int64_t qsb, int64_t qsh, const float *Pi, float mult, int Hq,
     int total_rows, float *q_rot, const int32_t *seq_lens, int B, int chunk_tokens,
-    int max_tokens, int32_t *chunk_prefix) {
+    int max_tokens, ScanSetup setup) {
   __shared__ __align__(16) float qs[2][128][NR];       // [buffer][coordinate][row]
   __shared__ float part_s[3][NR][128];
-  if (chunk_prefix != nullptr && blockIdx.x == gridDim.x - 1 && threadIdx.x < 32)
-    write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, chunk_prefix);
+  scan_setup(setup, seq_lens, B, chunk_tokens, max_tokens);
   const int tid = threadIdx.x, col = tid & 127, quarter = tid >> 7;
   float4 held[8];                                       // this thread's quarter of row `col` of Pi
   {
@@ -512,34 +529,34 @@ __global__ void __launch_bounds__(kRotThreads) rotate_q128_kernel(
 
 int launch_rotate_q(const void *q, int dtype, const int64_t *qs, const float *Pi, float scale,
                     int B, int Hq, int D, float *q_rot, const int32_t *seq_lens, int chunk_tokens,
-                    int max_tokens, int32_t *chunk_prefix, cudaStream_t stream) {
+                    int max_tokens, const ScanSetup &setup, cudaStream_t stream) {
   const int rows = B * Hq;
   // (two 512-thread blocks of the head_dim-128 kernel fit an SM, one of the general kernel)
   if (D == 128 && ((uintptr_t)Pi & 15) == 0 && rows >= 8 * 148)
     rotate_q128_kernel<8><<<std::min((rows + 7) / 8, 2 * 148), kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, rows, q_rot, seq_lens, B, chunk_tokens, max_tokens,
-        chunk_prefix);
+        setup);
   else if (D == 128 && ((uintptr_t)Pi & 15) == 0)
     rotate_q128_kernel<4><<<std::min((rows + 3) / 4, 2 * 148), kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, rows, q_rot, seq_lens, B, chunk_tokens, max_tokens,
-        chunk_prefix);
+        setup);
   else if (D % 16 == 0 && D <= 256 && ((uintptr_t)Pi & 15) == 0 && rows >= 8 * 148)
     // many rows: eight per pass halve the passes of the persistent blocks
     rotate_q_rows_kernel<8><<<std::min((rows + 7) / 8, 148), kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
-        max_tokens, chunk_prefix);
+        max_tokens, setup);
   else if (D % 16 == 0 && D <= 256 && ((uintptr_t)Pi & 15) == 0)
     rotate_q_rows_kernel<4><<<std::min((rows + 3) / 4, 148), kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
-        max_tokens, chunk_prefix);
+        max_tokens, setup);
   else if (rows % 4 == 0)
     rotate_q_kernel<4><<<rows / 4, kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
-        max_tokens, chunk_prefix);
+        max_tokens, setup);
   else
     rotate_q_kernel<1><<<rows, kRotThreads, 0, stream>>>(
         q, dtype, qs[0], qs[1], Pi, scale, Hq, D, rows, q_rot, seq_lens, B, chunk_tokens,
-        max_tokens, chunk_prefix);
+        max_tokens, setup);
   note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_decode rotate launch");
 }

@@ -33,6 +33,23 @@ struct DecodeParams {
   // counter block
   int32_t *work_counter;
   const int32_t *chunk_prefix;
+  // tensor-core path: the lookup tables in the layout the scan kernel keeps in
+  // shared memory, [index][key | value][lane] words, built by the rotation kernel
+  const uint32_t *lut;
+};
+
+// Table words the tensor-core scan wants for widths (bw_k, bw_v); 0 when the
+// pair has no tensor-core kernel.
+int mma_lut_words(int bw_k, int bw_v);
+
+// What the query-rotation launch also prepares for the tensor-core scan (all
+// optional): the exclusive prefix of ceil(seq_len / chunk_tokens) over the B
+// sequences (B + 1 ints), and the lookup tables.
+struct ScanSetup {
+  int32_t *chunk_prefix;
+  uint32_t *lut;
+  const float *cent_k, *cent_v;
+  int bw_k, bw_v, lut_words;
 };
 
 struct MergeParams {
@@ -49,11 +66,9 @@ struct MergeParams {
   int rank, world, head_offset;
 };
 
-// `chunk_prefix` (may be null): the launch also writes the exclusive prefix of
-// ceil(seq_len / chunk_tokens) over the B sequences (B + 1 ints).
 int launch_rotate_q(const void *q, int dtype, const int64_t *q_strides, const float *Pi,
                     float scale, int B, int Hq, int D, float *q_rot, const int32_t *seq_lens,
-                    int chunk_tokens, int max_tokens, int32_t *chunk_prefix, cudaStream_t stream);
+                    int chunk_tokens, int max_tokens, const ScanSetup &setup, cudaStream_t stream);
 int launch_decode_generic(const DecodeParams &p, cudaStream_t stream);
 int launch_merge(const MergeParams &p, int B, cudaStream_t stream);
 

@@ -2,7 +2,7 @@
 // for head_dim 128, key/value widths of 4, 6 or 8 bits (4/4, 4/6, 6/6, 8/8),
 // pages of 16, 32, 64, ... tokens and a GQA group of at most 8 query heads.
 //
-// One persistent CTA per SM, up to 16 warps.  A warp is an independent worker:
+// One persistent CTA per SM, up to 12 warps.  A warp is an independent worker:
 // it takes (sequence, kv head, chunk of tokens) items round-robin, streams the
 // chunk's 16-token tiles from HBM into its private shared-memory ring with
 // 16-byte cp.async copies (the next 32 tokens are in flight while the current
@@ -10,12 +10,16 @@
 //
 // Per 16-token tile, with the packed bytes never leaving registers/smem:
 //   scores   S^T[16 tok x 8 heads] = C_K[16 x 128] . Qrot^T   8 x mma.m16n8k16
-//   softmax  online, fp32, exp2 domain, max shared by shuffles
+//   softmax  online, fp32, exp2 domain, against a reference value that is only
+//            raised (and the state rescaled) when a score exceeds it: the
+//            common window costs one vote, no shuffles
 //   values   O^T[128 d x 8 heads] += C_V^T[128 x 16 tok] . P'^T   8 x mma
 // The fp16 operands C_K / C_V come from shared-memory tables replicated per
 // lane (every lookup of a warp is bank-conflict free) that start at shared
 // address 0x10000, so that the address of an entry is
-// 0x10000 | index << 8 | side << 7 | lane << 2 and needs no addition.
+// 0x10000 | index << 8 | side << 7 | lane << 2 and needs no addition.  The
+// tables are built once per call by the query-rotation kernel (into the
+// workspace) and pulled into shared memory by one bulk copy.
 //   4-bit: ONE lookup per packed byte (= two codes) into a 256-entry table of
 //     half2 {centroid[lo nibble], centroid[hi nibble]}; one byte-permute builds
 //     the address.  Keys: a byte holds two adjacent coordinates of one token,
@@ -48,9 +52,15 @@ constexpr int kIterTokens = kTileTokens * kTilesPerIter;
 constexpr uint32_t kLutAddr = 0x10000;                 // shared address of the tables
 constexpr uint32_t kPrefixAddr = 2048;                 // chunk prefix copy (>= dynamic smem base)
 constexpr int kPrefixMax = 1024;                       // entries (sequences + 1) it can hold
-constexpr uint32_t kRingLow = kPrefixAddr + 4 * kPrefixMax;   // rings start here
+constexpr uint32_t kLutBar = kPrefixAddr + 4 * kPrefixMax;    // mbarrier of the tables' copy
+constexpr uint32_t kRingLow = kLutBar + 64;            // rings start here
 constexpr uint32_t kSmemLimit = 227 * 1024;
 constexpr float kPreciseAbove = 8.0f;   // |score| (log2 units) that triggers fp32 rescoring
+constexpr float kSlack = 4.0f;          // the softmax reference is set this far above a new maximum
+constexpr int kWaitTries = 1 << 18;     // bound of the mbarrier wait (each try suspends for a while)
+// Worker warps per CTA.  Twelve warps of 168 registers beat sixteen of 128 on
+// every benchmark shape: the lookups of a warp overlap better than more warps do.
+constexpr int kMaxWarps = 12;
 
 constexpr int lut_entries(int bw) { return bw == 4 ? 256 : (1 << bw); }
 constexpr int cmax(int a, int b) { return a > b ? a : b; }
@@ -68,7 +78,7 @@ template <int BWK, int BWV> struct Cfg {
   static constexpr uint32_t kLutBytes = cmax(lut_entries(BWK), lut_entries(BWV)) * 256u;
   static constexpr int kRingsBelow = (int)((kLutAddr - kRingLow) / kRing);
   static constexpr int kRingsAbove = (int)((kSmemLimit - kLutAddr - kLutBytes) / kRing);
-  static constexpr int kWarps = cmin(16, kRingsBelow + kRingsAbove);
+  static constexpr int kWarps = cmin(kMaxWarps, kRingsBelow + kRingsAbove);
   static constexpr int kThreads = kWarps * 32;
   static constexpr size_t kDynamicSmem =
       kLutAddr + kLutBytes + (size_t)cmax(kWarps - kRingsBelow, 0) * kRing;
@@ -89,6 +99,43 @@ __device__ __forceinline__ void cp_async_commit() {
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
+// ---- asynchronous copies and their barriers -----------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded: false when the phase did not complete within kWaitTries tries.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < kWaitTries; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// `bytes` (a multiple of 16) from global `src` to this CTA's shared `dst`, both
+// 16-byte aligned; completion is counted on the mbarrier at `bar`.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -217,16 +264,16 @@ __device__ __forceinline__ void key_fragment(const uint32_t (&w0)[NW], const uin
 }
 
 // Value side of one tile: the lane holds coordinates 16g..16g+15 of tokens
-// 2t, 2t+1 (A, B) and 2t+8, 2t+9 (C, D).  MMA j (0..7) takes coordinates
-// 16g+2j (row g) and 16g+2j+1 (row g+8) of the output tile.
+// 2t, 2t+1 (A, B) and 2t+8, 2t+9 (C, D); `at` = address of its 16 codes of
+// token 2t.  MMA j (0..7) takes coordinates 16g+2j (row g) and 16g+2j+1 (row
+// g+8) of the output tile.
 template <int BW, int VROW>
-__device__ __forceinline__ void value_mmas(uint32_t vbase, int g, int t, uint32_t sel,
-                                           uint32_t pb0, uint32_t pb1, float (&acc)[8][4]) {
+__device__ __forceinline__ void value_mmas(uint32_t at, uint32_t sel, uint32_t pb0, uint32_t pb1,
+                                           float (&acc)[8][4]) {
   constexpr int NB8 = 2 * BW;                       // bytes of 16 codes
-  const uint32_t at = vbase + g * NB8;
   if constexpr (BW == 4) {
-    const uint2 wa = lds64(at + (2 * t) * VROW), wb = lds64(at + (2 * t + 1) * VROW);
-    const uint2 wc = lds64(at + (2 * t + 8) * VROW), wd = lds64(at + (2 * t + 9) * VROW);
+    const uint2 wa = lds64(at), wb = lds64(at + VROW);
+    const uint2 wc = lds64(at + 8 * VROW), wd = lds64(at + 9 * VROW);
     // byte j of lo_* : low nibbles of tokens (A | B << 4) at coordinate 16g+2j
     // byte j of hi_* : high nibbles, coordinate 16g+2j+1
     const uint32_t lo_ab[2] = {(wa.x & 0x0F0F0F0Fu) | ((wb.x << 4) & 0xF0F0F0F0u),
@@ -251,10 +298,10 @@ __device__ __forceinline__ void value_mmas(uint32_t vbase, int g, int t, uint32_
   } else {
     constexpr int NW = NB8 / 4;
     uint32_t wa[NW], wb[NW], wc[NW], wd[NW];
-    load_words<NB8>(at + (2 * t) * VROW, wa);
-    load_words<NB8>(at + (2 * t + 1) * VROW, wb);
-    load_words<NB8>(at + (2 * t + 8) * VROW, wc);
-    load_words<NB8>(at + (2 * t + 9) * VROW, wd);
+    load_words<NB8>(at, wa);
+    load_words<NB8>(at + VROW, wb);
+    load_words<NB8>(at + 8 * VROW, wc);
+    load_words<NB8>(at + 9 * VROW, wd);
     auto one = [&](auto jc) {
       constexpr int j = decltype(jc)::value;
       mma16816(acc[j],
@@ -271,24 +318,30 @@ __device__ __forceinline__ void value_mmas(uint32_t vbase, int g, int t, uint32_
 }
 
 // Scores of one tile: S^T fragment (rows g, g+8; heads 2t, 2t+1), unscaled.
+// `at` = address of the lane's 32 codes of token row g.  Even and odd
+// contraction steps accumulate separately (two chains of four dependent MMAs
+// instead of one of eight).
 template <int BW>
-__device__ __forceinline__ void key_mmas(uint32_t kbase, int g, int t, uint32_t sel,
-                                         const uint32_t (&qf)[8][2], float (&c)[4]) {
+__device__ __forceinline__ void key_mmas(uint32_t at, uint32_t sel, const uint32_t (&qf)[8][2],
+                                         float (&c)[4]) {
   constexpr int NB4 = 4 * BW;                       // bytes of 32 codes
   constexpr int NW = NB4 / 4, NB = 16 * BW;
   uint32_t w0[NW], w1[NW];
-  load_words<NB4>(kbase + g * NB + t * NB4, w0);
-  load_words<NB4>(kbase + (g + 8) * NB + t * NB4, w1);
+  load_words<NB4>(at, w0);
+  load_words<NB4>(at + 8 * NB, w1);
+  float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
   auto one = [&](auto ksc) {
     constexpr int ks = decltype(ksc)::value;
     uint32_t a[4];
     key_fragment<BW, ks>(w0, w1, sel, a);
-    mma16816(c, a[0], a[1], a[2], a[3], qf[ks][0], qf[ks][1]);
+    if constexpr (ks % 2 == 0) mma16816(c0, a[0], a[1], a[2], a[3], qf[ks][0], qf[ks][1]);
+    else mma16816(c1, a[0], a[1], a[2], a[3], qf[ks][0], qf[ks][1]);
   };
   one(std::integral_constant<int, 0>{}); one(std::integral_constant<int, 1>{});
   one(std::integral_constant<int, 2>{}); one(std::integral_constant<int, 3>{});
   one(std::integral_constant<int, 4>{}); one(std::integral_constant<int, 5>{});
   one(std::integral_constant<int, 6>{}); one(std::integral_constant<int, 7>{});
+  c[0] = c0[0] + c1[0]; c[1] = c0[1] + c1[1]; c[2] = c0[2] + c1[2]; c[3] = c0[3] + c1[3];
 }
 
 // fp32 scores of tile rows g and g+8 against two query rows (already rotated
@@ -325,26 +378,20 @@ template <int BWK, int BWV>
 __global__ void __launch_bounds__(Cfg<BWK, BWV>::kThreads, 1)
 decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   using C = Cfg<BWK, BWV>;
-  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  extern __shared__ __align__(128) uint8_t dyn_smem[];
   const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(dyn_smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   if (dyn_base > kPrefixAddr) {          // layout assumption broken: refuse, do not touch memory
-    if (p.status && tid == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+    if (p.status && tid == 0) atomicOr(p.status, WTQ_STATUS_LAYOUT);
     return;
   }
-
-  // ---- tables, one copy per lane: [index][K|V][lane] -------------------------
-  for (int e = tid; e < (int)(C::kLutBytes / 4); e += C::kThreads) {
-    const int index = e >> 6, side = (e >> 5) & 1;
-    const int bw = side ? BWV : BWK;
-    const float *cent = side ? p.v.centroids : p.k.centroids;
-    uint32_t v = 0;
-    if (bw == 4) v = pack_half2(cent[index & 15], cent[index >> 4]);
-    else if (index < (1 << bw)) v = pack_half2(cent[index], cent[index]);
-    sts32(kLutAddr + (uint32_t)e * 4u, v);
+  constexpr uint32_t kFull = 0xffffffffu;
+  if (tid == 0) {
+    mbar_init(kLutBar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  __syncthreads();
 
   const uint32_t ring = C::ring_address(warp);
   const uint32_t sel_k = 0x10000u | (uint32_t)(lane << 2);
@@ -371,17 +418,17 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
       int incl = n;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        const int up = __shfl_up_sync(kFull, incl, o);
         if (lane >= o) incl += up;
       }
       if (bb < p.B) sts32(kPrefixAddr + 4 * bb, (uint32_t)(running + incl - n));
-      running += __shfl_sync(0xffffffffu, incl, 31);
+      running += __shfl_sync(kFull, incl, 31);
     }
     if (lane == 0) sts32(kPrefixAddr + 4 * p.B, (uint32_t)running);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-      least = min(least, __shfl_xor_sync(0xffffffffu, least, o));
-      most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
+      least = min(least, __shfl_xor_sync(kFull, least, o));
+      most = max(most, __shfl_xor_sync(kFull, most, o));
     }
     // all sequences have the same number of chunks: items are equal, a fixed
     // round-robin balances them and the queue is not needed
@@ -391,18 +438,18 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   auto prefix_at = [&](int i) -> int {
     return prefix_local ? (int)lds32(kPrefixAddr + 4 * i) : p.chunk_prefix[i];
   };
-
-  // q_rot is written by the kernel launched just before this one; everything
-  // above overlapped with its tail.  The merge that follows may be scheduled as
-  // soon as SMs free up.
-  asm volatile("griddepcontrol.wait;\n" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  // The prefix in global memory, q_rot and the tables are written by the
+  // rotation kernel launched just before this one; pages, page table and
+  // lengths are older than that kernel's start (it is launched without the
+  // programmatic attribute), so the first window may be requested before the
+  // wait whenever the prefix is local.
+  if (!prefix_local) griddep_wait();
 
   // Items (one chunk of one kv head of one sequence; only chunks that exist are
   // numbered) are dealt round-robin, consecutive items to different CTAs; when
   // the sequences differ in length the last rounds come from a queue in global
   // memory instead, so that the warps finish together.  A queue item is
-  // requested one window before the current item ends: its round trip is
+  // requested two windows before the current item ends: its round trip is
   // hidden and the requests of different warps are spread in time.
   const int64_t items_live = (int64_t)prefix_at(p.B) * p.Hkv;
   const int workers = gridDim.x * C::kWarps;
@@ -420,6 +467,22 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   struct Item {
     int b, kvh, chunk, tok0, tok1;
     bool valid;
+  };
+  // The copies follow their own stream of items (one window ahead of the
+  // arithmetic), with what they need held per lane: the lane's share of the
+  // key and value rows of (kv head, page 0) and, in lanes 0..3, of the norm
+  // rows (0, 1: keys; 2, 3: values); entries `blk + lane` and `blk + 32 + lane`
+  // of the sequence's page-table row, so that a tile's page id costs a
+  // shuffle, not a dependent global load.
+  const uint8_t *src_k = nullptr, *src_v = nullptr, *src_n = nullptr;
+  const bool n_is_v = lane >= 2;
+  const uint32_t n_page = 2u * (uint32_t)(n_is_v ? p.v.norm_page_stride : p.k.norm_page_stride);
+  const uint32_t n_dst = n_is_v ? C::kOffNV + (lane - 2) * 16 : C::kOffNK + lane * 16;
+  int blk = 0, ids0 = -1, ids1 = -1;
+  const int32_t *table_row = p.page_table;
+  auto load_ids = [&]() {
+    ids0 = blk + lane < p.max_pages ? table_row[blk + lane] : -1;
+    ids1 = blk + 32 + lane < p.max_pages ? table_row[blk + 32 + lane] : -1;
   };
   auto decode_item = [&](int64_t item) -> Item {
     Item x{0, 0, 0, 0, 0, false};
@@ -445,41 +508,42 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     // (an empty chunk cannot be numbered by a consistent prefix; if it happens
     // the warp stops and says so rather than guess)
     if (!x.valid && p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+    if (x.valid) {                       // the copies move on to this item
+      src_k = p.k.pages + (int64_t)x.kvh * p.k.head_stride + lane * 16;
+      src_v = p.v.pages + (int64_t)x.kvh * p.v.head_stride + lane * 16;
+      src_n = n_is_v ? reinterpret_cast<const uint8_t *>(p.v.norms + (int64_t)x.kvh * p.v.norm_head_stride) + (lane - 2) * 16
+                     : reinterpret_cast<const uint8_t *>(p.k.norms + (int64_t)x.kvh * p.k.norm_head_stride) + lane * 16;
+      table_row = p.page_table + (int64_t)x.b * p.table_stride;
+      blk = (x.tok0 >> s_shift) & ~31;
+      load_ids();
+    }
     return x;
   };
 
-  // Copies of window `it` of item `x` into half `buf` of the ring: a tile's key
-  // rows and value rows are contiguous in HBM (16 rows of NB bytes); lane l
-  // moves 16-byte chunks l, l+32, ...; lanes 0..3 also move the norms.  Returns
-  // a bit per tile: set when the tile's page id was inside the pool.  Always
-  // commits one group.
-  // Page ids reach the copies through registers: lane l holds entry
-  // block + l of the page table row of sequence block_b, so that a window
-  // costs a shuffle, not a dependent global load, and the table is read once
-  // per 32 pages.
-  int block_b = -1, block_first = 0, block_ids = -1;
+  // Copies of window `it` of item `x` (the item decoded last) into half `buf` of
+  // the ring: a tile's key rows and value rows are contiguous in HBM (16 rows of
+  // NB bytes); lane l moves 16-byte chunks l, l+32, ...; lanes 0..3 also move
+  // the norms.  Returns a bit per tile: set when the tile's page id was inside
+  // the pool.  Always commits one group.
   auto issue = [&](const Item &x, int it, int buf) -> uint32_t {
     uint32_t loaded = 0;
-    const int32_t *table = p.page_table + (int64_t)x.b * p.table_stride;
 #pragma unroll
     for (int u = 0; u < kTilesPerIter; ++u) {
       const int tok = x.tok0 + it * kIterTokens + u * kTileTokens;
       if (x.valid && tok < x.tok1) {
         const int sub = tok & (S - 1);                     // first slot of the tile
         const int page = tok >> s_shift;
-        if (x.b != block_b || (page & ~31) != block_first) {      // warp-uniform
-          block_b = x.b;
-          block_first = page & ~31;
-          block_ids = block_first + lane < p.max_pages ? table[block_first + lane] : -1;
+        if (page - blk >= 64) {                            // beyond the ids held (very long chunks)
+          blk = page & ~31;
+          load_ids();
         }
-        const int pid = __shfl_sync(0xffffffffu, block_ids, page & 31);
+        const int rel = page - blk;
+        const int pid = __shfl_sync(kFull, rel < 32 ? ids0 : ids1, rel & 31);
         if (pid >= 0 && pid < p.P) {
           loaded |= 1u << u;
           const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-          const uint8_t *ks = p.k.pages + (int64_t)x.kvh * p.k.head_stride +
-                              (int64_t)pid * p.k.page_stride + (sub * C::NBK + lane * 16);
-          const uint8_t *vs = p.v.pages + (int64_t)x.kvh * p.v.head_stride +
-                              (int64_t)pid * p.v.page_stride + (sub * C::NBV + lane * 16);
+          const uint8_t *ks = src_k + (uint64_t)(uint32_t)pid * (uint32_t)p.k.page_stride + sub * C::NBK;
+          const uint8_t *vs = src_v + (uint64_t)(uint32_t)pid * (uint32_t)p.v.page_stride + sub * C::NBV;
 #pragma unroll
           for (int i = 0; i < C::NBK / 32; ++i) cp_async16(dst + lane * 16 + i * 512, ks + i * 512);
 #pragma unroll
@@ -489,14 +553,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
             else
               cp_async16(dst + C::kOffV + lane * 16 + i * 512, vs + i * 512);
           }
-          if (lane < 2)
-            cp_async16(dst + C::kOffNK + lane * 16,
-                       p.k.norms + (int64_t)x.kvh * p.k.norm_head_stride +
-                           (int64_t)pid * p.k.norm_page_stride + sub + lane * 8);
-          else if (lane < 4)
-            cp_async16(dst + C::kOffNV + (lane - 2) * 16,
-                       p.v.norms + (int64_t)x.kvh * p.v.norm_head_stride +
-                           (int64_t)pid * p.v.norm_page_stride + sub + (lane - 2) * 8);
+          if (lane < 4)
+            cp_async16(dst + n_dst, src_n + (uint64_t)(uint32_t)pid * n_page + sub * 2);
         } else if (p.status && lane == 0) {
           atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
         }
@@ -509,13 +567,27 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   // The ring is used as two halves; `windows` counts the windows this warp has
   // consumed, across items: the first window of the next item is requested
   // during the last window of the current one, so a new item starts on data
-  // that is already on its way.
-  Item cur = decode_item(__shfl_sync(0xffffffffu, next_item, 0));
-  uint32_t loaded_next = issue(cur, 0, 0);
+  // that is already on its way.  The next item itself is decoded one window
+  // earlier (its page ids are then on their way too) and asked for from the
+  // queue one window before that.
+  Item cur = decode_item(__shfl_sync(kFull, next_item, 0));
+  uint32_t loaded_next = prefix_local ? issue(cur, 0, 0) : 0u;
+  if (prefix_local) griddep_wait();
+  else loaded_next = issue(cur, 0, 0);
+  // The merge that follows may be scheduled as soon as SMs free up.
+  griddep_launch();
+  if (tid == 0) {
+    mbar_expect_tx(kLutBar, C::kLutBytes);
+    bulk_g2s(kLutAddr, p.lut, C::kLutBytes, kLutBar);
+  }
+  const bool tables_ok = mbar_wait(kLutBar, 0);
+  if (!tables_ok && p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_SCAN_TIMEOUT);
+
   int windows = 0;
-  for (int guard = 0; guard < (1 << 24) && cur.valid; ++guard) {   // bounded: never spins
+  for (int guard = 0; guard < (1 << 24) && cur.valid && tables_ok; ++guard) {   // bounded: never spins
     const int b = cur.b, kvh = cur.kvh, chunk = cur.chunk, tok0 = cur.tok0, tok1 = cur.tok1;
     Item nxt{0, 0, 0, 0, 0, false};
+    bool have_nxt = false, asked = false;
 
     // ---- query fragments: head g, coordinates 32t .. 32t+31 ----------------
     uint32_t qf[8][2];
@@ -533,19 +605,31 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     float acc[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // Softmax state of heads 2t, 2t+1: reference M (the probabilities are
+    // 2^(s - M), M >= every score seen), -M with -inf replaced by 0, the bound
+    // a window's scores (relative to M) must stay under to take the short path,
+    // and the sum of the probabilities.
+    float M0 = -INFINITY, M1 = -INFINITY, neg0 = 0.f, neg1 = 0.f;
+    float hi0 = -INFINITY, hi1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     const int n_iter = (tok1 - tok0 + kIterTokens - 1) / kIterTokens;
     for (int it = 0; it < n_iter; ++it) {
       const int buf = windows & 1;
-      if (it == (n_iter > 1 ? n_iter - 2 : 0) && lane == 0)
-        next_item = taken++ < static_rounds ? next_item + workers
-                                            : queue_base + atomicAdd(p.work_counter, 1);
+      if (!asked && it >= n_iter - 3) {
+        asked = true;
+        if (lane == 0)
+          next_item = taken++ < static_rounds ? next_item + workers
+                                              : queue_base + atomicAdd(p.work_counter, 1);
+      }
       const uint32_t loaded = loaded_next;
       if (it + 1 < n_iter) {
         loaded_next = issue(cur, it + 1, buf ^ 1);
+        if (it + 2 >= n_iter) {            // the copies are done with `cur`: on to the next item
+          nxt = decode_item(__shfl_sync(kFull, next_item, 0));
+          have_nxt = true;
+        }
       } else {
-        nxt = decode_item(__shfl_sync(0xffffffffu, next_item, 0));
+        if (!have_nxt) nxt = decode_item(__shfl_sync(kFull, next_item, 0));
         loaded_next = issue(nxt, 0, buf ^ 1);
       }
       cp_async_wait<1>();
@@ -558,92 +642,120 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
                          tok0 + (it + 1) * kIterTokens <= tok1;
       auto window = [&](auto masked_c) {
         constexpr bool MASKED = decltype(masked_c)::value;
+        const uint32_t slot0 = ring + (uint32_t)(buf * kTilesPerIter) * C::kSlot;
         // ---- scores of the tiles --------------------------------------------
-        float s[kTilesPerIter][4];
+        float c[kTilesPerIter][4], a[kTilesPerIter][4], nk[kTilesPerIter][2];
         bool ok[kTilesPerIter][2];
-        float big = 0.f;
 #pragma unroll
         for (int u = 0; u < kTilesPerIter; ++u) {
-          const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-          float c[4] = {0.f, 0.f, 0.f, 0.f};
-          key_mmas<BWK>(slot, g, t, sel_k, qf, c);
-          const float nk0 = lds_half(slot + C::kOffNK + g * 2);
-          const float nk1 = lds_half(slot + C::kOffNK + (g + 8) * 2);
-          c[0] *= nk0; c[1] *= nk0; c[2] *= nk1; c[3] *= nk1;
-          if constexpr (MASKED) {
-            const int tok = tok0 + it * kIterTokens + u * kTileTokens;
-            const bool page_ok = (loaded >> u) & 1u;
-            ok[u][0] = page_ok && tok + g < tok1;
-            ok[u][1] = page_ok && tok + g + 8 < tok1;
-            big = fmaxf(big, ok[u][0] ? fmaxf(fabsf(c[0]), fabsf(c[1])) : 0.f);
-            big = fmaxf(big, ok[u][1] ? fmaxf(fabsf(c[2]), fabsf(c[3])) : 0.f);
-            s[u][0] = ok[u][0] ? c[0] : -INFINITY;
-            s[u][1] = ok[u][0] ? c[1] : -INFINITY;
-            s[u][2] = ok[u][1] ? c[2] : -INFINITY;
-            s[u][3] = ok[u][1] ? c[3] : -INFINITY;
-          } else {
-            ok[u][0] = ok[u][1] = true;
-            big = fmaxf(big, fmaxf(fmaxf(fabsf(c[0]), fabsf(c[1])), fmaxf(fabsf(c[2]), fabsf(c[3]))));
-            s[u][0] = c[0]; s[u][1] = c[1]; s[u][2] = c[2]; s[u][3] = c[3];
-          }
+          const uint32_t slot = slot0 + u * C::kSlot;
+          key_mmas<BWK>(slot + g * C::NBK + t * (4 * BWK), sel_k, qf, c[u]);
+          nk[u][0] = lds_half(slot + C::kOffNK + g * 2);
+          nk[u][1] = lds_half(slot + C::kOffNK + (g + 8) * 2);
+          ok[u][0] = ok[u][1] = true;
         }
-
-        // ---- fp16 operands carry about 2^-11.5 of the score scale as error;
-        // when any score of this window is large (|s| > 8 in log2 units) its
-        // tiles are scored again in fp32 on the CUDA cores, so that large logits
-        // cost time, not accuracy.
-        if (__any_sync(0xffffffffu, big > kPreciseAbove)) {
-          const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
-          const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
-          const float *qa = q0 + (h0 ? 2 * t : 0) * 128, *qb = q0 + (h1 ? 2 * t + 1 : 0) * 128;
+        bool slow = true;
+        if constexpr (!MASKED) {
+          float top0 = -INFINITY, top1 = -INFINITY;
 #pragma unroll
           for (int u = 0; u < kTilesPerIter; ++u) {
-            const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-            const float4 d = precise_scores<BWK>(slot, slot + C::kOffNK, g, qa, qb, p.k.centroids);
-            s[u][0] = ok[u][0] ? (h0 ? d.x : 0.f) : -INFINITY;
-            s[u][1] = ok[u][0] ? (h1 ? d.y : 0.f) : -INFINITY;
-            s[u][2] = ok[u][1] ? (h0 ? d.z : 0.f) : -INFINITY;
-            s[u][3] = ok[u][1] ? (h1 ? d.w : 0.f) : -INFINITY;
+            a[u][0] = fmaf(c[u][0], nk[u][0], neg0); a[u][1] = fmaf(c[u][1], nk[u][0], neg1);
+            a[u][2] = fmaf(c[u][2], nk[u][1], neg0); a[u][3] = fmaf(c[u][3], nk[u][1], neg1);
+            top0 = fmaxf(top0, fmaxf(a[u][0], a[u][2]));
+            top1 = fmaxf(top1, fmaxf(a[u][1], a[u][3]));
+          }
+          slow = __any_sync(kFull, top0 > hi0 || top1 > hi1);
+        }
+        if (slow) {
+          // A score above the reference (or the first window, a large score, a
+          // partly filled window): exact scores, fp32 rescoring when they are
+          // large, new reference, state rescaled.
+          float s[kTilesPerIter][4];
+          float big = 0.f;
+#pragma unroll
+          for (int u = 0; u < kTilesPerIter; ++u) {
+            s[u][0] = c[u][0] * nk[u][0]; s[u][1] = c[u][1] * nk[u][0];
+            s[u][2] = c[u][2] * nk[u][1]; s[u][3] = c[u][3] * nk[u][1];
+            if constexpr (MASKED) {
+              const int tok = tok0 + it * kIterTokens + u * kTileTokens;
+              const bool page_ok = (loaded >> u) & 1u;
+              ok[u][0] = page_ok && tok + g < tok1;
+              ok[u][1] = page_ok && tok + g + 8 < tok1;
+            }
+            if (ok[u][0]) big = fmaxf(big, fmaxf(fabsf(s[u][0]), fabsf(s[u][1])));
+            if (ok[u][1]) big = fmaxf(big, fmaxf(fabsf(s[u][2]), fabsf(s[u][3])));
+          }
+          // fp16 operands carry about 2^-11.5 of the score scale as error; when
+          // any score of this window is large (|s| > 8 in log2 units) its tiles
+          // are scored again in fp32 on the CUDA cores, so that large logits
+          // cost time, not accuracy.
+          if (__any_sync(kFull, big > kPreciseAbove)) {
+            const float *q0 = p.q_rot + ((int64_t)b * p.Hq + kvh * p.n_rep) * 128;
+            const bool h0 = 2 * t < p.n_rep, h1 = 2 * t + 1 < p.n_rep;
+            const float *qa = q0 + (h0 ? 2 * t : 0) * 128, *qb = q0 + (h1 ? 2 * t + 1 : 0) * 128;
+#pragma unroll
+            for (int u = 0; u < kTilesPerIter; ++u) {
+              const uint32_t slot = slot0 + u * C::kSlot;
+              const float4 d = precise_scores<BWK>(slot, slot + C::kOffNK, g, qa, qb, p.k.centroids);
+              s[u][0] = h0 ? d.x : 0.f; s[u][1] = h1 ? d.y : 0.f;
+              s[u][2] = h0 ? d.z : 0.f; s[u][3] = h1 ? d.w : 0.f;
+            }
+          }
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+          for (int u = 0; u < kTilesPerIter; ++u) {
+            if (!ok[u][0]) s[u][0] = s[u][1] = -INFINITY;
+            if (!ok[u][1]) s[u][2] = s[u][3] = -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[u][0], s[u][2]));
+            mx1 = fmaxf(mx1, fmaxf(s[u][1], s[u][3]));
+          }
+#pragma unroll
+          for (int o = 4; o < 32; o <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, o));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, o));
+          }
+          const float n0 = mx0 > M0 ? mx0 + kSlack : M0;
+          const float n1 = mx1 > M1 ? mx1 + kSlack : M1;
+          if (__any_sync(kFull, n0 != M0 || n1 != M1)) {
+            // 2^(-inf - x) = 0 for the first window; an unchanged reference keeps 1
+            const float alpha0 = n0 != M0 ? ex2(M0 - n0) : 1.f;
+            const float alpha1 = n1 != M1 ? ex2(M1 - n1) : 1.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              acc[j][0] *= alpha0; acc[j][1] *= alpha1; acc[j][2] *= alpha0; acc[j][3] *= alpha1;
+            }
+            l0 *= alpha0;
+            l1 *= alpha1;
+            M0 = n0;
+            M1 = n1;
+          }
+          // exp2(-inf - -inf) is defined as 0: with nothing seen the base is 0
+          neg0 = M0 == -INFINITY ? 0.f : -M0;
+          neg1 = M1 == -INFINITY ? 0.f : -M1;
+          // short path while every score stays under the reference and under the
+          // rescoring threshold; never when the running maximum is a large
+          // negative number (all scores are large then)
+          hi0 = (M0 == -INFINITY || M0 - kSlack < -kPreciseAbove) ? -INFINITY
+                                                                 : fminf(0.f, kPreciseAbove - M0);
+          hi1 = (M1 == -INFINITY || M1 - kSlack < -kPreciseAbove) ? -INFINITY
+                                                                 : fminf(0.f, kPreciseAbove - M1);
+#pragma unroll
+          for (int u = 0; u < kTilesPerIter; ++u) {
+            a[u][0] = s[u][0] + neg0; a[u][1] = s[u][1] + neg1;
+            a[u][2] = s[u][2] + neg0; a[u][3] = s[u][3] + neg1;
           }
         }
-
-        // ---- running max per head (heads 2t, 2t+1), shared over the 8 rows --
-        float mx[2] = {m_run[0], m_run[1]};
-#pragma unroll
-        for (int u = 0; u < kTilesPerIter; ++u) {
-          mx[0] = fmaxf(mx[0], fmaxf(s[u][0], s[u][2]));
-          mx[1] = fmaxf(mx[1], fmaxf(s[u][1], s[u][3]));
-        }
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
-          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
-        }
-        // exp2(-inf - -inf) is defined as 0: with nothing seen the base is 0
-        const float base0 = mx[0] == -INFINITY ? 0.f : mx[0];
-        const float base1 = mx[1] == -INFINITY ? 0.f : mx[1];
-        const float alpha0 = ex2(m_run[0] - base0), alpha1 = ex2(m_run[1] - base1);
-        if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            acc[j][0] *= alpha0; acc[j][1] *= alpha1; acc[j][2] *= alpha0; acc[j][3] *= alpha1;
-          }
-          l_run[0] *= alpha0;
-          l_run[1] *= alpha1;
-        }
-        m_run[0] = mx[0];
-        m_run[1] = mx[1];
 
         // ---- values of the tiles --------------------------------------------
 #pragma unroll
         for (int u = 0; u < kTilesPerIter; ++u) {
-          const uint32_t slot = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
+          const uint32_t slot = slot0 + u * C::kSlot;
           const float nv0 = lds_half(slot + C::kOffNV + g * 2);
           const float nv1 = lds_half(slot + C::kOffNV + (g + 8) * 2);
-          const float p0 = ex2(s[u][0] - base0), p1 = ex2(s[u][1] - base1);
-          const float p2 = ex2(s[u][2] - base0), p3 = ex2(s[u][3] - base1);
-          l_run[0] += p0 + p2;
-          l_run[1] += p1 + p3;
+          const float p0 = ex2(a[u][0]), p1 = ex2(a[u][1]);
+          const float p2 = ex2(a[u][2]), p3 = ex2(a[u][3]);
+          l0 += p0 + p2;
+          l1 += p1 + p3;
           // rows g / g+8 of P' (token x head) -> B fragment (token pairs of head g)
           uint32_t r0 = pack_half2(p0 * nv0, p1 * nv0), r1 = pack_half2(p2 * nv1, p3 * nv1);
           if constexpr (MASKED) {
@@ -651,7 +763,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
             r1 = ok[u][1] ? r1 : 0u;
           }
           const uint32_t pb0 = movmatrix_trans(r0), pb1 = movmatrix_trans(r1);
-          value_mmas<BWV, C::kVRow>(slot + C::kOffV, g, t, sel_v, pb0, pb1, acc);
+          value_mmas<BWV, C::kVRow>(slot + C::kOffV + g * (2 * BWV) + (2 * t) * C::kVRow, sel_v, pb0,
+                                    pb1, acc);
         }
       };
       if (whole) window(std::false_type{});
@@ -663,8 +776,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     // ---- partial state of this chunk ---------------------------------------
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
-      l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
-      l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
+      l0 += __shfl_xor_sync(kFull, l0, o);
+      l1 += __shfl_xor_sync(kFull, l1, o);
     }
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -675,8 +788,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) dst[j] = make_float2(acc[j][e], acc[j][2 + e]);
         if (g == 0) {
-          p.part_m[row] = m_run[e];
-          p.part_l[row] = l_run[e];
+          p.part_m[row] = e ? M1 : M0;
+          p.part_l[row] = e ? l1 : l0;
         }
       }
     }
@@ -1075,14 +1188,25 @@ bool mma_eligible(const DecodeParams &p) {
          p.k.page_stride % 16 == 0 && p.k.head_stride % 16 == 0 && p.v.page_stride % 16 == 0 &&
          p.v.head_stride % 16 == 0 && p.k.norm_page_stride % 8 == 0 &&
          p.k.norm_head_stride % 8 == 0 && p.v.norm_page_stride % 8 == 0 &&
-         p.v.norm_head_stride % 8 == 0 && aligned(p.q_rot) && aligned(p.part_acc);
+         p.v.norm_head_stride % 8 == 0 && aligned(p.q_rot) && aligned(p.part_acc) &&
+         aligned(p.lut) && p.k.page_stride < (int64_t)1 << 31 && p.v.page_stride < (int64_t)1 << 31 &&
+         p.k.norm_page_stride < (int64_t)1 << 30 && p.v.norm_page_stride < (int64_t)1 << 30;
+}
+
+int mma_lut_words(int bw_k, int bw_v) {
+  if (bw_k == 4 && bw_v == 4) return Cfg<4, 4>::kLutBytes / 4;
+  if (bw_k == 4 && bw_v == 6) return Cfg<4, 6>::kLutBytes / 4;
+  if (bw_k == 6 && bw_v == 6) return Cfg<6, 6>::kLutBytes / 4;
+  if (bw_k == 8 && bw_v == 8) return Cfg<8, 8>::kLutBytes / 4;
+  return 0;
 }
 
 // Tokens per chunk for `splits` chunks over `max_tokens`, a multiple of 32.
 int mma_chunk_tokens(int max_tokens, int splits) {
+  constexpr int kGrain = 2 * kTileTokens;
   int per = (max_tokens + splits - 1) / splits;
-  per = (per + kIterTokens - 1) / kIterTokens * kIterTokens;
-  return per < kIterTokens ? kIterTokens : per;
+  per = (per + kGrain - 1) / kGrain * kGrain;
+  return per < kGrain ? kGrain : per;
 }
 
 template <int BWK, int BWV>

@@ -77,8 +77,14 @@ class PeerExchange:
 
     SPIN_LIMIT = 4_000_000            # polls of ~100 ns: gives up after a fraction of a second
 
-    def __init__(self, batch: int, q_heads: int, head_dim: int, dtype, device, group=None):
+    def __init__(self, batch: int, q_heads: int, head_dim: int, dtype, device, group=None,
+                 spin_limit: int | None = None):
+        """`spin_limit`: polls of a peer's flag before the wait gives up (default
+        SPIN_LIMIT); size it to the rank skew the serving loop expects.  After a
+        timeout the buffer still holds the late rank's previous rows: the result
+        of a step is valid only while `status` is zero (`check()`)."""
         import torch.distributed._symmetric_memory as symm_mem
+        self.spin_limit = int(spin_limit) if spin_limit else self.SPIN_LIMIT
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         if q_heads % self.world:
@@ -123,7 +129,7 @@ class PeerExchange:
             self._desc = ex
             self._wait = _lib.lib().wtq_exchange_wait
             self._wait_args = (self.flags.data_ptr(), self.world, self.step_dev.data_ptr(),
-                               self.SPIN_LIMIT, self.status.data_ptr())
+                               self.spin_limit, self.status.data_ptr())
         return self._desc
 
     def wait(self) -> None:
@@ -143,6 +149,19 @@ class PeerExchange:
         from . import _lib
         return bool(int(self.status.item()) & _lib.STATUS_EXCHANGE_TIMEOUT)
 
+    def check(self) -> None:
+        """Raise if any wait since the last check gave up (synchronises with
+        the device: call it where the caller syncs anyway, e.g. before sampling).
+        The status word is cleared so that later steps are judged on their own."""
+        from . import _lib
+        word = int(self.status.item())
+        if word:
+            self.status.zero_()
+            raise _lib.BackendError(
+                f"output exchange: status {word:#x} after step {self.step} (bit "
+                f"{_lib.STATUS_EXCHANGE_TIMEOUT}: a peer's rows did not arrive within "
+                f"{self.spin_limit} polls; the gathered buffer holds stale rows for it)")
+
 
 class TensorParallelDecode:
     """One rank's side of the sharded decode step.
@@ -155,25 +174,38 @@ class TensorParallelDecode:
 
     def __init__(self, q_local: torch.Tensor, kv, scale: float, q_heads: int, *, group=None,
                  num_splits: int | None = None, check_page_ids: bool = True,
-                 exchange: str = "nccl"):
+                 exchange: str = "nccl", spin_limit: int | None = None):
         """`exchange="nccl"`: scan, then `all_gather_into_tensor` and a permuting
         copy.  `exchange="peer"`: the merge kernel writes every rank's buffer
         itself (`PeerExchange`); shapes without a tensor-core kernel fall back to
-        "nccl" (see `self.exchange`)."""
+        "nccl" (see `self.exchange`).  The choice is agreed on by all ranks: the
+        peer form is used only if every rank could set it up, so no rank ends up
+        in a collective the others never enter."""
         from .packed_attention_cuda import DecodePlan
         B, hq, _, D = q_local.shape
         self.exchange = exchange
         self.peer = None
         if exchange == "peer":
+            why = ""
             try:
-                self.peer = PeerExchange(B, q_heads, D, q_local.dtype, q_local.device, group)
-                if hq != self.peer.hq:
-                    raise ValueError(f"expected {self.peer.hq} local query heads, got {hq}")
-                self.plan = DecodePlan(q_local, kv, scale, num_splits=num_splits,
-                                       out=self.peer.full[0][:, :hq], check_page_ids=check_page_ids)
-                self.plan.run_exchange(self.peer.descriptor(), dry_run=True)
+                # (symmetric-memory set-up is itself collective: every rank enters it)
+                self.peer = PeerExchange(B, q_heads, D, q_local.dtype, q_local.device, group,
+                                         spin_limit=spin_limit)
             except _lib_error() as exc:
-                self.peer, self.exchange = None, f"nccl (peer exchange unavailable: {exc})"
+                self.peer, why = None, f"{type(exc).__name__}: {exc}"
+            if self.peer is not None:
+                try:
+                    if hq != self.peer.hq:
+                        raise ValueError(f"expected {self.peer.hq} local query heads, got {hq}")
+                    self.plan = DecodePlan(q_local, kv, scale, num_splits=num_splits,
+                                           out=self.peer.full[0][:, :hq],
+                                           check_page_ids=check_page_ids)
+                    self.plan.run_exchange(self.peer.descriptor(), dry_run=True)
+                except _lib_error() as exc:
+                    why = f"{type(exc).__name__}: {exc}"
+            if not _all_ranks_agree(why == "", q_local.device, group):
+                self.peer = None
+                self.exchange = f"nccl (peer exchange unavailable on some rank{': ' + why if why else ''})"
         if self.peer is None:
             self.heads = HeadGather(B, q_heads, D, q_local.dtype, q_local.device, group)
             if hq != self.heads.hq:
@@ -181,14 +213,38 @@ class TensorParallelDecode:
             self.plan = DecodePlan(q_local, kv, scale, num_splits=num_splits, out=self.heads.local,
                                    check_page_ids=check_page_ids)
 
-    def step(self) -> torch.Tensor:
+    def step(self, check: bool = False) -> torch.Tensor:
+        """One decode step; returns the full (B, Hq, 1, D) output.  On the peer
+        path the wait for the other ranks' rows is bounded: if a rank is later
+        than `spin_limit` polls the wait gives up, sets the status word and the
+        returned buffer still holds that rank's previous rows.  The output is
+        therefore valid only while the status is zero: pass `check=True` (one
+        device synchronisation per step) or call `check()` at the next point
+        where the caller synchronises anyway; both raise `BackendError`."""
         if self.peer is None:
             self.plan.run()
             return self.heads.gather()
         self.peer.step += 1
         self.plan.run_exchange(self.peer.descriptor())
         self.peer.wait()
+        if check:
+            self.peer.check()
         return self.peer.result(self.peer.step)
+
+    def check(self) -> None:
+        """Raise `BackendError` if a bounded wait gave up since the last check."""
+        if self.peer is not None:
+            self.peer.check()
+
+
+def _all_ranks_agree(ok: bool, device, group) -> bool:
+    """True when `ok` holds on every rank of the group (one small all-reduce)."""
+    if not dist.is_initialized():
+        return ok
+    dev = device if dist.get_backend(group) == "nccl" else "cpu"
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(int(flag.item()))
 
 
 def _lib_error():
