@@ -63,25 +63,26 @@ def test_argument_errors_are_reported_without_a_gpu(library):
 def test_auto_splits_fills_the_last_round_of_worker_warps():
     """`wtq_decode_auto_splits` is host arithmetic (148 SMs assumed without a
     GPU): for the tensor-core shapes it picks the chunk, a multiple of 32 tokens
-    in [64, 512], whose items just fill a whole number of rounds of the 2368
-    worker warps; the answers for the benchmark shapes are pinned."""
+    in [64, 1024], whose items just fill a whole number of rounds of the 1776
+    worker warps (12 per SM); the answers for the benchmark shapes are pinned."""
     from winnow_b200 import _lib
     f = _lib.lib().wtq_decode_auto_splits
-    workers = 148 * 16
+    workers = 148 * 12
 
     def items(B, Hkv, ctx, S, bk, bv, n_rep=4):
         splits = f(B, Hkv * n_rep, Hkv, 128, -(-ctx // S), S, bk, bv)
         assert 1 <= splits <= 1024
         chunk = -(-(-(-ctx // splits)) // 32) * 32
-        assert 64 <= chunk <= 512 or ctx <= 64
+        assert 64 <= chunk <= 1024 or ctx <= 64
         return splits, B * Hkv * -(-ctx // chunk)
 
-    assert items(16, 8, 8192, 16, 4, 4) == (18, 2304)           # config 2: one round
-    assert items(16, 4, 8192, 16, 4, 4) == (37, 2368)           # its 2-GPU shard: exactly one round
-    assert items(16, 1, 8192, 16, 4, 4)[0] == 128               # its 8-GPU shard: 64-token chunks
-    assert items(16, 8, 32768, 16, 4, 4) == (74, 4 * workers)   # 32k context: four full rounds
-    assert items(1, 8, 131072, 64, 4, 4, n_rep=8)[0] == 293     # config 4
-    assert items(128, 8, 32768, 16, 4, 6)[0] == 64              # config 5: 512-token chunks
+    assert items(16, 8, 8192, 16, 4, 4) == (13, 1664)           # config 2: one round, 94 % full
+    assert items(16, 4, 8192, 16, 4, 4) == (26, 1664)           # its 2-GPU shard
+    assert items(16, 1, 8192, 16, 4, 4)[0] == 86                # its 8-GPU shard: 96-token chunks
+    splits, n = items(16, 8, 32768, 16, 4, 4)                   # 32k context: three rounds
+    assert splits == 41 and 2.9 < n / workers <= 3.0
+    assert items(1, 8, 131072, 64, 4, 4, n_rep=8) == (216, 1728)   # config 4: one round
+    assert items(128, 8, 32768, 16, 4, 6)[0] == 38              # config 5: 864-token chunks
     # degenerate sizes stay in range
     assert f(1, 4, 1, 128, 1, 16, 4, 4) >= 1
     assert f(0, 4, 1, 128, 1, 16, 4, 4) == 1

@@ -1,7 +1,9 @@
 """wtq_decode_static, the decode entry point for hosts that may not allocate
 device memory (its workspace is an array inside the library image): called
 through the C ABI twice in a row and compared with wtq_decode, which takes a
-caller-allocated workspace.  Collected last on purpose."""
+caller-allocated workspace, and with the CPU oracle; the device's free memory
+must be the same before the first and after the last call.  Collected last on
+purpose."""
 import ctypes
 
 import pytest
@@ -17,10 +19,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def call_static(q, kv, scale, num_splits=0):
-    """One call of wtq_decode_static with raw pointers; allocates only `out`."""
+def call_static(q, kv, scale, num_splits=0, out=None):
+    """One call of wtq_decode_static with raw pointers; allocates only `out`
+    (nothing when the caller passes it)."""
     B, Hq, _, D = q.shape
-    out = torch.empty_like(q)
+    out = torch.empty_like(q) if out is None else out
     k_side = _side(kv.k_pages, kv.k_norms, kv.k_quant)
     v_side = _side(kv.v_pages, kv.v_norms, kv.v_quant)
     rc = _lib.lib().wtq_decode_static(
@@ -40,18 +43,25 @@ def test_static_workspace_matches_wtq_decode_twice(name):
     kv, scale = to_device(okv, DEV), orc.default_scale(c.D)
     qd = q.to(DEV)
     expect = packed_decode_attention(qd, kv, scale)
-    rc, first = call_static(qd, kv, scale)
+    q2 = (qd * 0.5 + 0.25).contiguous()
+    expect2 = packed_decode_attention(q2, kv, scale, num_splits=2)
+    outs = [torch.empty_like(qd), torch.empty_like(qd)]
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    rc, first = call_static(qd, kv, scale, out=outs[0])
     assert rc == 0, _lib.lib().wtq_last_error()
     # second call: other data and another split count over the same array, which
     # still holds the first call's partial states
-    q2 = (qd * 0.5 + 0.25).contiguous()
-    expect2 = packed_decode_attention(q2, kv, scale, num_splits=2)
-    rc, second = call_static(q2, kv, scale, num_splits=2)
+    rc, second = call_static(q2, kv, scale, num_splits=2, out=outs[1])
     assert rc == 0, _lib.lib().wtq_last_error()
     torch.cuda.synchronize()
-    for got, ref in ((first, expect), (second, expect2)):
+    # the property the entry point exists for: no device memory was taken
+    assert torch.cuda.mem_get_info()[0] == free_before
+    for got, ref, qq in ((first, expect, q), (second, expect2, q * 0.5 + 0.25)):
         assert torch.isfinite(got).all()
         assert (got.float() - ref.float()).abs().max().item() <= 2e-3
+        oracle = orc.tiled_attention(qq, okv, scale)
+        assert (got.float().cpu() - oracle).abs().max().item() <= 2e-3
     for b, L in enumerate(c.lens):
         if L == 0:
             assert (first[b] == 0).all() and (second[b] == 0).all()
@@ -63,8 +73,8 @@ def test_static_workspace_refuses_oversized_calls():
     assert cap == 16 << 20
     # 64 sequences x 64 heads x 256 splits of fp32 partial rows is far beyond 16 MiB
     assert lib.wtq_decode_workspace_bytes(64, 64, 8, 128, 8192, 16, 256) > cap
-    q = torch.zeros(64, 64, 1, 128, device=DEV)
-    c = cases.ATTENTION_CASES[5]
+    q = torch.zeros(64, 64, 1, 128, device=DEV)          # 64 query heads over the case's 8 kv heads
+    c = next(x for x in cases.ATTENTION_CASES if x.name == "val_long")      # 32 / 8 heads
     _, okv, _ = oracle_case(c)
     kv = to_device(okv, DEV)
     big_table = torch.full((64, 8192), -1, dtype=torch.int32, device=DEV)

@@ -133,6 +133,31 @@ extern "C" size_t wtq_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int 
   return workspace_for(B, Hq, Hkv, D, splits);
 }
 
+// Argument checks shared by every decode entry point; nothing is launched or
+// queued before they pass.
+int wtq::decode_validate(const void *q, int dtype, const int64_t q_strides[2], const void *out,
+                         const int64_t out_strides[2], bool has_exchange, const wtq_side_t *k_side,
+                         const wtq_side_t *v_side, const int32_t *page_table,
+                         const int32_t *seq_lens, int B, int Hq, int Hkv, int D, int S, int P,
+                         int max_pages) {
+  if (B < 0 || Hq < 1 || Hkv < 1 || S < 1 || P < 1 || max_pages < 1)
+    return fail(WTQ_ERR_ARG, "wtq_decode: bad sizes");
+  if (Hq % Hkv) return fail(WTQ_ERR_ARG, "wtq_decode: Hq=%d is not a multiple of Hkv=%d", Hq, Hkv);
+  if (D < 1 || D > 256) return fail(WTQ_ERR_ARG, "wtq_decode: need 1 <= head_dim <= 256");
+  if (dtype < WTQ_F32 || dtype > WTQ_BF16) return fail(WTQ_ERR_ARG, "wtq_decode: bad dtype");
+  if (!k_side || !v_side || !q_strides || !out_strides)
+    return fail(WTQ_ERR_ARG, "wtq_decode: null descriptor");
+  for (const wtq_side_t *w : {k_side, v_side}) {
+    if (!width_supported(w->bw) || (D * w->bw) % 8)
+      return fail(WTQ_ERR_ARG, "wtq_decode: bit width %d unsupported for head_dim %d", w->bw, D);
+    if (!w->pages || !w->norms || !w->Pi || !w->centroids)
+      return fail(WTQ_ERR_ARG, "wtq_decode: null pages, norms, Pi or centroids");
+  }
+  if (B > 0 && (!q || (!out && !has_exchange) || !page_table || !seq_lens))
+    return fail(WTQ_ERR_ARG, "wtq_decode: null input");
+  return WTQ_OK;
+}
+
 static int decode_common(const void *q, int dtype, const int64_t q_strides[2], void *out,
                          const int64_t out_strides[2], const wtq_exchange_t *exchange,
                          const wtq_side_t *k_side, const wtq_side_t *v_side,
@@ -141,22 +166,14 @@ static int decode_common(const void *q, int dtype, const int64_t q_strides[2], v
                          int num_splits, void *workspace, size_t workspace_bytes, int32_t *status,
                          void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  if (B < 0 || Hq < 1 || Hkv < 1 || S < 1 || P < 1 || max_pages < 1)
-    return fail(WTQ_ERR_ARG, "wtq_decode: bad sizes");
-  if (Hq % Hkv) return fail(WTQ_ERR_ARG, "wtq_decode: Hq=%d is not a multiple of Hkv=%d", Hq, Hkv);
-  if (D < 1 || D > 256) return fail(WTQ_ERR_ARG, "wtq_decode: need 1 <= head_dim <= 256");
-  if (dtype < WTQ_F32 || dtype > WTQ_BF16) return fail(WTQ_ERR_ARG, "wtq_decode: bad dtype");
-  if (!k_side || !v_side || !q_strides || !out_strides)
-    return fail(WTQ_ERR_ARG, "wtq_decode: null descriptor");
-  for (const wtq_side_t *w : {k_side, v_side})
-    if (!width_supported(w->bw) || (D * w->bw) % 8)
-      return fail(WTQ_ERR_ARG, "wtq_decode: bit width %d unsupported for head_dim %d", w->bw, D);
+  if (int rc = decode_validate(q, dtype, q_strides, out, out_strides, exchange != nullptr, k_side,
+                               v_side, page_table, seq_lens, B, Hq, Hkv, D, S, P, max_pages))
+    return rc;
   if (B == 0) return WTQ_OK;
   DecodeParams p;
-  if (!fill_side(p.k, *k_side, D) || !fill_side(p.v, *v_side, D))
-    return fail(WTQ_ERR_ARG, "wtq_decode: null pages, norms, Pi or centroids");
-  if (!q || (!out && !exchange) || !page_table || !seq_lens || !workspace)
-    return fail(WTQ_ERR_ARG, "wtq_decode: null input");
+  fill_side(p.k, *k_side, D);
+  fill_side(p.v, *v_side, D);
+  if (!workspace) return fail(WTQ_ERR_ARG, "wtq_decode: null workspace");
   const int splits = num_splits > 0 ? clamp_splits(num_splits, max_pages, S)
                                     : wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S,
                                                              k_side->bw, v_side->bw);

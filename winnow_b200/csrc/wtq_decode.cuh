@@ -66,6 +66,13 @@ struct MergeParams {
   int rank, world, head_offset;
 };
 
+// Argument checks of the decode entry points (wtq_api.cu); WTQ_OK or an error
+// code with the text set.
+int decode_validate(const void *q, int dtype, const int64_t q_strides[2], const void *out,
+                    const int64_t out_strides[2], bool has_exchange, const wtq_side_t *k_side,
+                    const wtq_side_t *v_side, const int32_t *page_table, const int32_t *seq_lens,
+                    int B, int Hq, int Hkv, int D, int S, int P, int max_pages);
+
 int launch_rotate_q(const void *q, int dtype, const int64_t *q_strides, const float *Pi,
                     float scale, int B, int Hq, int D, float *q_rot, const int32_t *seq_lens,
                     int chunk_tokens, int max_tokens, const ScanSetup &setup, cudaStream_t stream);

@@ -38,6 +38,7 @@
 // Reference schedule being reproduced: turboquant_kv/packed_attention.py:
 // 260-334 (tiled online softmax), split merge :328-334.
 #include <algorithm>
+#include <cstdlib>
 #include <type_traits>
 
 #include "wtq_decode.cuh"
@@ -53,7 +54,8 @@ constexpr uint32_t kLutAddr = 0x10000;                 // shared address of the 
 constexpr uint32_t kPrefixAddr = 2048;                 // chunk prefix copy (>= dynamic smem base)
 constexpr int kPrefixMax = 1024;                       // entries (sequences + 1) it can hold
 constexpr uint32_t kLutBar = kPrefixAddr + 4 * kPrefixMax;    // mbarrier of the tables' copy
-constexpr uint32_t kRingLow = kLutBar + 64;            // rings start here
+constexpr uint32_t kFifoAddr = kLutBar + 64;           // per warp: four decoded items of 32 bytes
+constexpr uint32_t kRingLow = kFifoAddr + 16 * 128;    // rings start here
 constexpr uint32_t kSmemLimit = 227 * 1024;
 constexpr float kPreciseAbove = 8.0f;   // |score| (log2 units) that triggers fp32 rescoring
 constexpr float kSlack = 4.0f;          // the softmax reference is set this far above a new maximum
@@ -74,7 +76,7 @@ template <int BWK, int BWV> struct Cfg {
   static constexpr int kOffNK = kOffV + kTileTokens * kVRow;
   static constexpr int kOffNV = kOffNK + 32;
   static constexpr int kSlot = kOffNV + 32;
-  static constexpr int kRing = 2 * kTilesPerIter * kSlot;       // two iterations per warp
+  static constexpr int kRing = 2 * kTilesPerIter * kSlot;       // two windows per warp
   static constexpr uint32_t kLutBytes = cmax(lut_entries(BWK), lut_entries(BWV)) * 256u;
   static constexpr int kRingsBelow = (int)((kLutAddr - kRingLow) / kRing);
   static constexpr int kRingsAbove = (int)((kSmemLimit - kLutAddr - kLutBytes) / kRing);
@@ -165,6 +167,11 @@ __device__ __forceinline__ float lds_half(uint32_t a) {
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(a), "r"(v) : "memory");
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -191,8 +198,11 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 // ---- table lookups ----------------------------------------------------------
 // `sel` carries 0x10000, the side bit (values: 0x80) and the lane's bank.
 // 4-bit: entry of byte K (0..3) of `word`, a half2 of the byte's two codes.
+template <int K> __device__ __forceinline__ uint32_t lut_addr(uint32_t word, uint32_t sel) {
+  return __byte_perm(word, sel, 0x7604 | (K << 4));
+}
 template <int K> __device__ __forceinline__ uint32_t lut_byte(uint32_t word, uint32_t sel) {
-  return lds32(__byte_perm(word, sel, 0x7604 | (K << 4)));
+  return lds32(lut_addr<K>(word, sel));
 }
 // 6/8-bit: entry {c, c} of code I of the bit stream held in w[0..NW).
 template <int BW, int I, int NW>
@@ -276,24 +286,34 @@ __device__ __forceinline__ void value_mmas(uint32_t at, uint32_t sel, uint32_t p
     const uint2 wc = lds64(at + 8 * VROW), wd = lds64(at + 9 * VROW);
     // byte j of lo_* : low nibbles of tokens (A | B << 4) at coordinate 16g+2j
     // byte j of hi_* : high nibbles, coordinate 16g+2j+1
-    const uint32_t lo_ab[2] = {(wa.x & 0x0F0F0F0Fu) | ((wb.x << 4) & 0xF0F0F0F0u),
-                               (wa.y & 0x0F0F0F0Fu) | ((wb.y << 4) & 0xF0F0F0F0u)};
-    const uint32_t hi_ab[2] = {((wa.x >> 4) & 0x0F0F0F0Fu) | (wb.x & 0xF0F0F0F0u),
-                               ((wa.y >> 4) & 0x0F0F0F0Fu) | (wb.y & 0xF0F0F0F0u)};
-    const uint32_t lo_cd[2] = {(wc.x & 0x0F0F0F0Fu) | ((wd.x << 4) & 0xF0F0F0F0u),
-                               (wc.y & 0x0F0F0F0Fu) | ((wd.y << 4) & 0xF0F0F0F0u)};
-    const uint32_t hi_cd[2] = {((wc.x >> 4) & 0x0F0F0F0Fu) | (wd.x & 0xF0F0F0F0u),
-                               ((wc.y >> 4) & 0x0F0F0F0Fu) | (wd.y & 0xF0F0F0F0u)};
+    auto up4 = [](uint32_t x) { return x << 4; };
+    auto down4 = [](uint32_t x) { return x >> 4; };
+    const uint32_t lo_ab[2] = {(wa.x & 0x0F0F0F0Fu) | (up4(wb.x) & 0xF0F0F0F0u),
+                               (wa.y & 0x0F0F0F0Fu) | (up4(wb.y) & 0xF0F0F0F0u)};
+    const uint32_t hi_ab[2] = {(down4(wa.x) & 0x0F0F0F0Fu) | (wb.x & 0xF0F0F0F0u),
+                               (down4(wa.y) & 0x0F0F0F0Fu) | (wb.y & 0xF0F0F0F0u)};
+    const uint32_t lo_cd[2] = {(wc.x & 0x0F0F0F0Fu) | (up4(wd.x) & 0xF0F0F0F0u),
+                               (wc.y & 0x0F0F0F0Fu) | (up4(wd.y) & 0xF0F0F0F0u)};
+    const uint32_t hi_cd[2] = {(down4(wc.x) & 0x0F0F0F0Fu) | (wd.x & 0xF0F0F0F0u),
+                               (down4(wc.y) & 0x0F0F0F0Fu) | (wd.y & 0xF0F0F0F0u)};
+    // The sixteen table addresses of a half are formed first, then the sixteen
+    // lookups are issued, then the four MMAs: a lookup never waits for the
+    // byte-permute that builds its own address.
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      mma16816(acc[4 * h + 0], lut_byte<0>(lo_ab[h], sel), lut_byte<0>(hi_ab[h], sel),
-               lut_byte<0>(lo_cd[h], sel), lut_byte<0>(hi_cd[h], sel), pb0, pb1);
-      mma16816(acc[4 * h + 1], lut_byte<1>(lo_ab[h], sel), lut_byte<1>(hi_ab[h], sel),
-               lut_byte<1>(lo_cd[h], sel), lut_byte<1>(hi_cd[h], sel), pb0, pb1);
-      mma16816(acc[4 * h + 2], lut_byte<2>(lo_ab[h], sel), lut_byte<2>(hi_ab[h], sel),
-               lut_byte<2>(lo_cd[h], sel), lut_byte<2>(hi_cd[h], sel), pb0, pb1);
-      mma16816(acc[4 * h + 3], lut_byte<3>(lo_ab[h], sel), lut_byte<3>(hi_ab[h], sel),
-               lut_byte<3>(lo_cd[h], sel), lut_byte<3>(hi_cd[h], sel), pb0, pb1);
+      uint32_t ad[4][4], f[4][4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t src = q == 0 ? lo_ab[h] : q == 1 ? hi_ab[h] : q == 2 ? lo_cd[h] : hi_cd[h];
+        ad[0][q] = lut_addr<0>(src, sel); ad[1][q] = lut_addr<1>(src, sel);
+        ad[2][q] = lut_addr<2>(src, sel); ad[3][q] = lut_addr<3>(src, sel);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) f[j][q] = lds32(ad[j][q]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mma16816(acc[4 * h + j], f[j][0], f[j][1], f[j][2], f[j][3], pb0, pb1);
     }
   } else {
     constexpr int NW = NB8 / 4;
@@ -329,19 +349,43 @@ __device__ __forceinline__ void key_mmas(uint32_t at, uint32_t sel, const uint32
   uint32_t w0[NW], w1[NW];
   load_words<NB4>(at, w0);
   load_words<NB4>(at + 8 * NB, w1);
-  float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-  auto one = [&](auto ksc) {
-    constexpr int ks = decltype(ksc)::value;
-    uint32_t a[4];
-    key_fragment<BW, ks>(w0, w1, sel, a);
-    if constexpr (ks % 2 == 0) mma16816(c0, a[0], a[1], a[2], a[3], qf[ks][0], qf[ks][1]);
-    else mma16816(c1, a[0], a[1], a[2], a[3], qf[ks][0], qf[ks][1]);
-  };
-  one(std::integral_constant<int, 0>{}); one(std::integral_constant<int, 1>{});
-  one(std::integral_constant<int, 2>{}); one(std::integral_constant<int, 3>{});
-  one(std::integral_constant<int, 4>{}); one(std::integral_constant<int, 5>{});
-  one(std::integral_constant<int, 6>{}); one(std::integral_constant<int, 7>{});
-  c[0] = c0[0] + c1[0]; c[1] = c0[1] + c1[1]; c[2] = c0[2] + c1[2]; c[3] = c0[3] + c1[3];
+  constexpr int kChains = 2;
+  float cc[kChains][4];
+#pragma unroll
+  for (int i = 0; i < kChains; ++i) cc[i][0] = cc[i][1] = cc[i][2] = cc[i][3] = 0.f;
+  if constexpr (BW == 4) {
+    // per word of the two rows: eight addresses, eight lookups, two MMAs
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t ad[8], f[8];
+      ad[0] = lut_addr<0>(w0[j], sel); ad[1] = lut_addr<0>(w1[j], sel);
+      ad[2] = lut_addr<1>(w0[j], sel); ad[3] = lut_addr<1>(w1[j], sel);
+      ad[4] = lut_addr<2>(w0[j], sel); ad[5] = lut_addr<2>(w1[j], sel);
+      ad[6] = lut_addr<3>(w0[j], sel); ad[7] = lut_addr<3>(w1[j], sel);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = lds32(ad[i]);
+      mma16816(cc[0], f[0], f[1], f[2], f[3], qf[2 * j][0], qf[2 * j][1]);
+      mma16816(cc[1], f[4], f[5], f[6], f[7], qf[2 * j + 1][0], qf[2 * j + 1][1]);
+    }
+  } else {
+    auto one = [&](auto ksc) {
+      constexpr int ks = decltype(ksc)::value;
+      uint32_t a[4];
+      key_fragment<BW, ks>(w0, w1, sel, a);
+      mma16816(cc[ks % kChains], a[0], a[1], a[2], a[3], qf[ks][0], qf[ks][1]);
+    };
+    one(std::integral_constant<int, 0>{}); one(std::integral_constant<int, 1>{});
+    one(std::integral_constant<int, 2>{}); one(std::integral_constant<int, 3>{});
+    one(std::integral_constant<int, 4>{}); one(std::integral_constant<int, 5>{});
+    one(std::integral_constant<int, 6>{}); one(std::integral_constant<int, 7>{});
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float v = cc[0][e];
+#pragma unroll
+    for (int i = 1; i < kChains; ++i) v += cc[i][e];
+    c[e] = v;
+  }
 }
 
 // fp32 scores of tile rows g and g+8 against two query rows (already rotated
@@ -374,7 +418,7 @@ __device__ __noinline__ float4 precise_scores(uint32_t kbase, uint32_t nk_addr, 
   return make_float4(d0 * nk0, d1 * nk0, d2 * nk1, d3 * nk1);
 }
 
-template <int BWK, int BWV>
+template <int BWK, int BWV, bool S16>
 __global__ void __launch_bounds__(Cfg<BWK, BWV>::kThreads, 1)
 decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   using C = Cfg<BWK, BWV>;
@@ -396,8 +440,11 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   const uint32_t ring = C::ring_address(warp);
   const uint32_t sel_k = 0x10000u | (uint32_t)(lane << 2);
   const uint32_t sel_v = sel_k | 0x80u;
-  const int S = p.S;
-  const int s_shift = 31 - __clz(S);                 // S is a power of two (checked by the host)
+  // tiles per page (a power of two) as a shift and a mask; both are constants
+  // for 16-token pages, the common case
+  const int S = S16 ? 16 : p.S;
+  const int ts = S16 ? 0 : 27 - __clz(S);
+  const int tmask = S16 ? 0 : (S >> 4) - 1;
   const int chunks = p.num_splits;
 
   // Exclusive prefix of chunks per sequence, in shared memory when the batch
@@ -448,9 +495,7 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   // Items (one chunk of one kv head of one sequence; only chunks that exist are
   // numbered) are dealt round-robin, consecutive items to different CTAs; when
   // the sequences differ in length the last rounds come from a queue in global
-  // memory instead, so that the warps finish together.  A queue item is
-  // requested two windows before the current item ends: its round trip is
-  // hidden and the requests of different warps are spread in time.
+  // memory instead, so that the warps finish together.
   const int64_t items_live = (int64_t)prefix_at(p.B) * p.Hkv;
   const int workers = gridDim.x * C::kWarps;
   const bool fixed_rounds = prefix_local && lds32(kPrefixAddr + 4 * (kPrefixMax - 1)) != 0u;
@@ -463,31 +508,43 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   int taken = 1;                                      // items this warp has been dealt
   int next_item = warp * gridDim.x + blockIdx.x;
 
-  // One work item: a chunk of one kv head of one sequence.
-  struct Item {
-    int b, kvh, chunk, tok0, tok1;
-    bool valid;
-  };
-  // The copies follow their own stream of items (one window ahead of the
-  // arithmetic), with what they need held per lane: the lane's share of the
-  // key and value rows of (kv head, page 0) and, in lanes 0..3, of the norm
-  // rows (0, 1: keys; 2, 3: values); entries `blk + lane` and `blk + 32 + lane`
-  // of the sequence's page-table row, so that a tile's page id costs a
-  // shuffle, not a dependent global load.
+  // ---- the copies -------------------------------------------------------------
+  // They run one window (two tiles) ahead of the arithmetic, through item
+  // boundaries, along their own stream of items: an item is decoded when the
+  // stream reaches it and handed to the arithmetic through a small queue in
+  // shared memory; the item after it is asked for at once (from the static deal
+  // or the global queue), so that round trip hides behind a whole item of copies.
+  // Every instruction here competes with the table lookups for the integer
+  // pipe, which is what bounds this kernel, so the per-tile work is kept to a
+  // page-id shuffle, one range check and three multiply-adds for addresses:
+  //   src_*      the lane's share of the key rows, value rows and (lanes 0..3)
+  //              norm rows of (kv head, page 0);
+  //   ids0/ids1  entries first_page + lane and first_page + 32 + lane of the
+  //              sequence's page-table row (a chunk spans at most 64 pages; longer
+  //              ones reload);
+  //   cs_tile    tiles of the item requested so far, cs_tiles its tile count,
+  //              cs_t0 the tile of the chunk's first token inside its page.
   const uint8_t *src_k = nullptr, *src_v = nullptr, *src_n = nullptr;
   const bool n_is_v = lane >= 2;
   const uint32_t n_page = 2u * (uint32_t)(n_is_v ? p.v.norm_page_stride : p.k.norm_page_stride);
   const uint32_t n_dst = n_is_v ? C::kOffNV + (lane - 2) * 16 : C::kOffNK + lane * 16;
-  int blk = 0, ids0 = -1, ids1 = -1;
+  const uint32_t k_page = (uint32_t)p.k.page_stride, v_page = (uint32_t)p.v.page_stride;
+  int ids0 = -1, ids1 = -1, ids_first = 0;
   const int32_t *table_row = p.page_table;
+  int cs_tile = 0, cs_tiles = 0, cs_t0 = 0;
+  bool cs_valid = false;
+  const uint32_t fifo = kFifoAddr + (uint32_t)warp * 128;
+  int fifo_w = 0, fifo_r = 0;
+  uint32_t bad = 0;                   // tiles whose page id was refused: bit 2 * half + tile
   auto load_ids = [&]() {
-    ids0 = blk + lane < p.max_pages ? table_row[blk + lane] : -1;
-    ids1 = blk + 32 + lane < p.max_pages ? table_row[blk + 32 + lane] : -1;
+    ids0 = ids_first + lane < p.max_pages ? table_row[ids_first + lane] : -1;
+    ids1 = ids_first + 32 + lane < p.max_pages ? table_row[ids_first + 32 + lane] : -1;
   };
-  auto decode_item = [&](int64_t item) -> Item {
-    Item x{0, 0, 0, 0, 0, false};
-    if (item >= items_live) return x;
-    x.kvh = (int)(item % p.Hkv);
+  auto next_stream_item = [&]() {
+    const int64_t item = __shfl_sync(kFull, next_item, 0);
+    cs_valid = false;
+    if (item >= items_live) return;
+    const int kvh = (int)(item % p.Hkv);
     const int flat = (int)(item / p.Hkv);                   // chunk number over all sequences
     int lo = 0, hi = p.B;                                   // last b with prefix[b] <= flat
     while (hi - lo > 1) {
@@ -495,85 +552,91 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
       if (prefix_at(mid) <= flat) lo = mid;
       else hi = mid;
     }
-    x.b = lo;
-    x.chunk = flat - prefix_at(lo);
+    const int chunk = flat - prefix_at(lo);
     int L = p.seq_lens[lo];
     if (L > p.max_pages * S) {
       L = p.max_pages * S;
       if (p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
     }
-    x.tok0 = x.chunk * chunk_tokens;
-    x.tok1 = min(L, x.tok0 + chunk_tokens);
-    x.valid = x.tok0 < x.tok1;
-    // (an empty chunk cannot be numbered by a consistent prefix; if it happens
-    // the warp stops and says so rather than guess)
-    if (!x.valid && p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
-    if (x.valid) {                       // the copies move on to this item
-      src_k = p.k.pages + (int64_t)x.kvh * p.k.head_stride + lane * 16;
-      src_v = p.v.pages + (int64_t)x.kvh * p.v.head_stride + lane * 16;
-      src_n = n_is_v ? reinterpret_cast<const uint8_t *>(p.v.norms + (int64_t)x.kvh * p.v.norm_head_stride) + (lane - 2) * 16
-                     : reinterpret_cast<const uint8_t *>(p.k.norms + (int64_t)x.kvh * p.k.norm_head_stride) + lane * 16;
-      table_row = p.page_table + (int64_t)x.b * p.table_stride;
-      blk = (x.tok0 >> s_shift) & ~31;
-      load_ids();
+    const int tok0 = chunk * chunk_tokens, tok1 = min(L, tok0 + chunk_tokens);
+    if (tok0 >= tok1) {
+      // (an empty chunk cannot be numbered by a consistent prefix; if it happens
+      // the warp stops and says so rather than guess)
+      if (p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_POSITION);
+      return;
     }
-    return x;
+    cs_valid = true;
+    cs_tile = 0;
+    cs_tiles = (tok1 - tok0 + kTileTokens - 1) / kTileTokens;
+    cs_t0 = (tok0 & (S - 1)) >> 4;
+    src_k = p.k.pages + (int64_t)kvh * p.k.head_stride + lane * 16;
+    src_v = p.v.pages + (int64_t)kvh * p.v.head_stride + lane * 16;
+    src_n = n_is_v ? reinterpret_cast<const uint8_t *>(p.v.norms + (int64_t)kvh * p.v.norm_head_stride) + (lane - 2) * 16
+                   : reinterpret_cast<const uint8_t *>(p.k.norms + (int64_t)kvh * p.k.norm_head_stride) + lane * 16;
+    table_row = p.page_table + (int64_t)lo * p.table_stride;
+    ids_first = tok0 >> (ts + 4);
+    load_ids();
+    if (lane == 0) {
+      const uint32_t e = fifo + (uint32_t)(fifo_w & 3) * 32;
+      sts32(e, (uint32_t)lo); sts32(e + 4, (uint32_t)kvh); sts32(e + 8, (uint32_t)chunk);
+      sts32(e + 12, (uint32_t)tok0); sts32(e + 16, (uint32_t)tok1);
+      next_item = taken++ < static_rounds ? next_item + workers
+                                          : queue_base + atomicAdd(p.work_counter, 1);
+    }
+    ++fifo_w;
   };
-
-  // Copies of window `it` of item `x` (the item decoded last) into half `buf` of
-  // the ring: a tile's key rows and value rows are contiguous in HBM (16 rows of
-  // NB bytes); lane l moves 16-byte chunks l, l+32, ...; lanes 0..3 also move
-  // the norms.  Returns a bit per tile: set when the tile's page id was inside
-  // the pool.  Always commits one group.
-  auto issue = [&](const Item &x, int it, int buf) -> uint32_t {
-    uint32_t loaded = 0;
+  // Requests the next window of the stream into the ring half at `ibase`
+  // (`ihalf` = 0 or 1 names it in `bad`).  Always commits one group.
+  uint32_t ibase = ring;
+  int ihalf = 0;
+  auto issue_one = [&]() {
+    if (bad) bad &= ~(3u << (2 * ihalf));
+    if (cs_valid) {
 #pragma unroll
-    for (int u = 0; u < kTilesPerIter; ++u) {
-      const int tok = x.tok0 + it * kIterTokens + u * kTileTokens;
-      if (x.valid && tok < x.tok1) {
-        const int sub = tok & (S - 1);                     // first slot of the tile
-        const int page = tok >> s_shift;
-        if (page - blk >= 64) {                            // beyond the ids held (very long chunks)
-          blk = page & ~31;
-          load_ids();
-        }
-        const int rel = page - blk;
-        const int pid = __shfl_sync(kFull, rel < 32 ? ids0 : ids1, rel & 31);
-        if (pid >= 0 && pid < p.P) {
-          loaded |= 1u << u;
-          const uint32_t dst = ring + (uint32_t)(buf * kTilesPerIter + u) * C::kSlot;
-          const uint8_t *ks = src_k + (uint64_t)(uint32_t)pid * (uint32_t)p.k.page_stride + sub * C::NBK;
-          const uint8_t *vs = src_v + (uint64_t)(uint32_t)pid * (uint32_t)p.v.page_stride + sub * C::NBV;
-#pragma unroll
-          for (int i = 0; i < C::NBK / 32; ++i) cp_async16(dst + lane * 16 + i * 512, ks + i * 512);
-#pragma unroll
-          for (int i = 0; i < C::NBV / 32; ++i) {
-            if constexpr (BWV == 4)      // chunk c -> padded row c/4, quarter c%4
-              cp_async16(dst + C::kOffV + (g + 8 * i) * C::kVRow + t * 16, vs + i * 512);
-            else
-              cp_async16(dst + C::kOffV + lane * 16 + i * 512, vs + i * 512);
+      for (int u = 0; u < kTilesPerIter; ++u) {
+        const int n = cs_tile + u;
+        if (n < cs_tiles) {
+          const int q = cs_t0 + n;
+          int rel = S16 ? q : q >> ts;                      // page of the tile, from the item's first
+          const uint32_t sub = S16 ? 0u : (uint32_t)(q & tmask) << 4;
+          if (rel >= 64) {                                  // beyond the ids held (very long chunks)
+            ids_first += rel & ~31;
+            cs_t0 -= (rel & ~31) << ts;
+            rel &= 31;
+            load_ids();
           }
-          if (lane < 4)
-            cp_async16(dst + n_dst, src_n + (uint64_t)(uint32_t)pid * n_page + sub * 2);
-        } else if (p.status && lane == 0) {
-          atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+          const int pid = __shfl_sync(kFull, rel < 32 ? ids0 : ids1, rel);
+          if ((uint32_t)pid < (uint32_t)p.P) {
+            const uint32_t dst = ibase + u * C::kSlot;
+            const uint8_t *ks = src_k + (uint64_t)(uint32_t)pid * k_page + sub * C::NBK;
+            const uint8_t *vs = src_v + (uint64_t)(uint32_t)pid * v_page + sub * C::NBV;
+#pragma unroll
+            for (int i = 0; i < C::NBK / 32; ++i) cp_async16(dst + lane * 16 + i * 512, ks + i * 512);
+#pragma unroll
+            for (int i = 0; i < C::NBV / 32; ++i) {
+              if constexpr (BWV == 4)      // chunk c -> padded row c/4, quarter c%4
+                cp_async16(dst + C::kOffV + (g + 8 * i) * C::kVRow + t * 16, vs + i * 512);
+              else
+                cp_async16(dst + C::kOffV + lane * 16 + i * 512, vs + i * 512);
+            }
+            if (lane < 4)
+              cp_async16(dst + n_dst, src_n + (uint64_t)(uint32_t)pid * n_page + sub * 2);
+          } else {
+            bad |= 1u << (2 * ihalf + u);
+            if (p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+          }
         }
       }
+      cs_tile += kTilesPerIter;
+      if (cs_tile >= cs_tiles) next_stream_item();
     }
     cp_async_commit();
-    return loaded;
+    ibase = 2 * ring + kTilesPerIter * C::kSlot - ibase;     // the other half
+    ihalf ^= 1;
   };
-
-  // The ring is used as two halves; `windows` counts the windows this warp has
-  // consumed, across items: the first window of the next item is requested
-  // during the last window of the current one, so a new item starts on data
-  // that is already on its way.  The next item itself is decoded one window
-  // earlier (its page ids are then on their way too) and asked for from the
-  // queue one window before that.
-  Item cur = decode_item(__shfl_sync(kFull, next_item, 0));
-  uint32_t loaded_next = prefix_local ? issue(cur, 0, 0) : 0u;
+  next_stream_item();
+  issue_one();
   if (prefix_local) griddep_wait();
-  else loaded_next = issue(cur, 0, 0);
   // The merge that follows may be scheduled as soon as SMs free up.
   griddep_launch();
   if (tid == 0) {
@@ -583,11 +646,14 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   const bool tables_ok = mbar_wait(kLutBar, 0);
   if (!tables_ok && p.status && lane == 0) atomicOr(p.status, WTQ_STATUS_SCAN_TIMEOUT);
 
-  int windows = 0;
-  for (int guard = 0; guard < (1 << 24) && cur.valid && tables_ok; ++guard) {   // bounded: never spins
-    const int b = cur.b, kvh = cur.kvh, chunk = cur.chunk, tok0 = cur.tok0, tok1 = cur.tok1;
-    Item nxt{0, 0, 0, 0, 0, false};
-    bool have_nxt = false, asked = false;
+  uint32_t cbase = ring;              // ring half consumed next
+  int chalf = 0;
+  for (int guard = 0; guard < (1 << 24) && fifo_r < fifo_w && tables_ok; ++guard) {   // bounded
+    __syncwarp();
+    const uint32_t entry = fifo + (uint32_t)(fifo_r & 3) * 32;
+    const int b = (int)lds32(entry), kvh = (int)lds32(entry + 4), chunk = (int)lds32(entry + 8);
+    const int tok0 = (int)lds32(entry + 12), tok1 = (int)lds32(entry + 16);
+    ++fifo_r;
 
     // ---- query fragments: head g, coordinates 32t .. 32t+31 ----------------
     uint32_t qf[8][2];
@@ -612,37 +678,16 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
     float M0 = -INFINITY, M1 = -INFINITY, neg0 = 0.f, neg1 = 0.f;
     float hi0 = -INFINITY, hi1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
+    // A window whose 32 tokens all exist on pages that were found needs no
+    // masks; only the last window of a chunk (or a refused page id) takes the
+    // masked form of the same code.
+    const int n_full = (tok1 - tok0) / kIterTokens;            // windows without a ragged end
     const int n_iter = (tok1 - tok0 + kIterTokens - 1) / kIterTokens;
-    for (int it = 0; it < n_iter; ++it) {
-      const int buf = windows & 1;
-      if (!asked && it >= n_iter - 3) {
-        asked = true;
-        if (lane == 0)
-          next_item = taken++ < static_rounds ? next_item + workers
-                                              : queue_base + atomicAdd(p.work_counter, 1);
-      }
-      const uint32_t loaded = loaded_next;
-      if (it + 1 < n_iter) {
-        loaded_next = issue(cur, it + 1, buf ^ 1);
-        if (it + 2 >= n_iter) {            // the copies are done with `cur`: on to the next item
-          nxt = decode_item(__shfl_sync(kFull, next_item, 0));
-          have_nxt = true;
-        }
-      } else {
-        if (!have_nxt) nxt = decode_item(__shfl_sync(kFull, next_item, 0));
-        loaded_next = issue(nxt, 0, buf ^ 1);
-      }
-      cp_async_wait<1>();
-      __syncwarp();
-
-      // A window whose 32 tokens all exist on pages that were found needs no
-      // masks; only the last window of a sequence (or a bad page id) takes the
-      // masked form of the same code.
-      const bool whole = loaded == (1u << kTilesPerIter) - 1u &&
-                         tok0 + (it + 1) * kIterTokens <= tok1;
+    int wtok = tok0;                                           // first token of the window
+    uint32_t loaded = 3u;
       auto window = [&](auto masked_c) {
         constexpr bool MASKED = decltype(masked_c)::value;
-        const uint32_t slot0 = ring + (uint32_t)(buf * kTilesPerIter) * C::kSlot;
+        const uint32_t slot0 = cbase;
         // ---- scores of the tiles --------------------------------------------
         float c[kTilesPerIter][4], a[kTilesPerIter][4], nk[kTilesPerIter][2];
         bool ok[kTilesPerIter][2];
@@ -661,8 +706,8 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
           for (int u = 0; u < kTilesPerIter; ++u) {
             a[u][0] = fmaf(c[u][0], nk[u][0], neg0); a[u][1] = fmaf(c[u][1], nk[u][0], neg1);
             a[u][2] = fmaf(c[u][2], nk[u][1], neg0); a[u][3] = fmaf(c[u][3], nk[u][1], neg1);
-            top0 = fmaxf(top0, fmaxf(a[u][0], a[u][2]));
-            top1 = fmaxf(top1, fmaxf(a[u][1], a[u][3]));
+            top0 = max3(top0, a[u][0], a[u][2]);
+            top1 = max3(top1, a[u][1], a[u][3]);
           }
           slow = __any_sync(kFull, top0 > hi0 || top1 > hi1);
         }
@@ -677,7 +722,7 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
             s[u][0] = c[u][0] * nk[u][0]; s[u][1] = c[u][1] * nk[u][0];
             s[u][2] = c[u][2] * nk[u][1]; s[u][3] = c[u][3] * nk[u][1];
             if constexpr (MASKED) {
-              const int tok = tok0 + it * kIterTokens + u * kTileTokens;
+              const int tok = wtok + u * kTileTokens;
               const bool page_ok = (loaded >> u) & 1u;
               ok[u][0] = page_ok && tok + g < tok1;
               ok[u][1] = page_ok && tok + g + 8 < tok1;
@@ -767,10 +812,20 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
                                     pb1, acc);
         }
       };
-      if (whole) window(std::false_type{});
-      else window(std::true_type{});
-      __syncwarp();       // every lane is done with this half before it is refilled
-      ++windows;
+    for (int it = 0; it < n_iter; ++it) {
+      issue_one();
+      cp_async_wait<1>();
+      __syncwarp();
+      if (it < n_full && bad == 0u) {
+        window(std::false_type{});
+      } else {
+        loaded = ~(bad >> (2 * chalf)) & 3u;
+        window(std::true_type{});
+      }
+      __syncwarp();       // every lane is done with this half of the ring before it is refilled
+      cbase = 2 * ring + kTilesPerIter * C::kSlot - cbase;
+      chalf ^= 1;
+      wtok += kIterTokens;
     }
 
     // ---- partial state of this chunk ---------------------------------------
@@ -793,7 +848,6 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
         }
       }
     }
-    cur = nxt;
   }
   cp_async_wait<0>();
 }
@@ -1218,9 +1272,12 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
   cudaGetDevice(&dev);
   bool &opted_in = opted_in_dev[dev & 63];
   if (!opted_in) {
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<BWK, BWV>,
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<BWK, BWV, true>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)C::kDynamicSmem);
+    if (e != cudaSuccess) return check_cuda(e, "wtq_decode: shared memory opt-in");
+    e = cudaFuncSetAttribute(decode_mma_kernel<BWK, BWV, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kDynamicSmem);
     if (e != cudaSuccess) return check_cuda(e, "wtq_decode: shared memory opt-in");
     e = cudaFuncSetAttribute(merge_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              128 * 128 * (int)sizeof(float));
@@ -1245,7 +1302,8 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
   cfg.attrs = &pdl;
   cfg.numAttrs = 1;
   profile_mark_begin(stream);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<BWK, BWV>, p, chunk_tokens);
+  cudaError_t e = p.S == 16 ? cudaLaunchKernelEx(&cfg, decode_mma_kernel<BWK, BWV, true>, p, chunk_tokens)
+                            : cudaLaunchKernelEx(&cfg, decode_mma_kernel<BWK, BWV, false>, p, chunk_tokens);
   profile_mark_end(stream);
   if (e != cudaSuccess) return check_cuda(e, "wtq_decode mma launch");
   const int num_groups_all = p.B * p.Hkv;

@@ -10,7 +10,7 @@
 // entry point is ever called.
 #include <mutex>
 
-#include "wtq_common.cuh"
+#include "wtq_decode.cuh"
 
 namespace {
 
@@ -53,17 +53,21 @@ extern "C" int wtq_decode_static(const void *q, int dtype, const int64_t q_strid
                                  int64_t table_stride, const int32_t *seq_lens, float scale, int B,
                                  int Hq, int Hkv, int D, int S, int P, int max_pages,
                                  int num_splits, int32_t *status, void *stream) {
-  if (B < 0 || Hq < 1 || Hkv < 1 || D < 1 || S < 1 || max_pages < 1 || !k_side || !v_side)
-    return wtq::fail(WTQ_ERR_ARG, "wtq_decode_static: bad sizes or null descriptor");
-  const int splits = num_splits > 0
-                         ? num_splits
-                         : wtq_decode_auto_splits(B, Hq, Hkv, D, max_pages, S, k_side->bw, v_side->bw);
-  const size_t need = wtq_decode_workspace_bytes(B, Hq, Hkv, D, max_pages, S, splits);
+  // every argument is checked before anything is queued on the stream
+  if (int rc = wtq::decode_validate(q, dtype, q_strides, out, out_strides, false, k_side, v_side,
+                                    page_table, seq_lens, B, Hq, Hkv, D, S, P, max_pages))
+    return rc;
+  if (!out) return wtq::fail(WTQ_ERR_ARG, "wtq_decode_static: null output");
+  // num_splits goes through unchanged (<= 0: the library's own choice), so this
+  // entry point runs the same schedule as wtq_decode; the size asked for is the
+  // one wtq_decode_workspace_bytes reports for that argument.
+  const size_t need = wtq_decode_workspace_bytes(B, Hq, Hkv, D, max_pages, S, num_splits);
   if (need > kStaticScratchBytes)
     return wtq::fail(WTQ_ERR_WORKSPACE,
                      "wtq_decode_static: this call needs %zu bytes of scratch, the built-in array "
                      "holds %zu; lower num_splits or use wtq_decode with your own workspace",
                      need, kStaticScratchBytes);
+  if (B == 0) return WTQ_OK;
   void *scratch = nullptr;
   if (int rc = scratch_for_current_device(&scratch)) return rc;
   // The array keeps whatever the previous call left.  Only the leading counter
@@ -71,6 +75,6 @@ extern "C" int wtq_decode_static(const void *q, int dtype, const int64_t q_strid
   cudaError_t e = cudaMemsetAsync(scratch, 0, wtq_decode_counter_bytes(B, Hkv), (cudaStream_t)stream);
   if (e != cudaSuccess) return wtq::check_cuda(e, "wtq_decode_static: clearing counters");
   return wtq_decode(q, dtype, q_strides, out, out_strides, k_side, v_side, page_table, table_stride,
-                    seq_lens, scale, B, Hq, Hkv, D, S, P, max_pages, splits, scratch,
+                    seq_lens, scale, B, Hq, Hkv, D, S, P, max_pages, num_splits, scratch,
                     kStaticScratchBytes, status, stream);
 }
