@@ -33,10 +33,6 @@ from winnow_b200 import workloads  # noqa: E402
 
 METRIC = "packed_decode_attn_us_per_step"
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the scan kernel
-# over its algorithmic bytes, from an ncu capture of the default workload (its
-# summary is kept under profiles/; the excess is the chunk states it writes)
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 145.5 / 138.7
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -215,14 +211,42 @@ def time_cpu_port(q, okv, scale, reps):
 # arms
 # --------------------------------------------------------------------------
 def run_ours(args):
-    from winnow_b200 import _lib
-    from winnow_b200.packed_attention_cuda import (DecodePlan, decode_workspace,
-                                                   packed_decode_attention)
-
+    """Main workload (the JSON line's top-level keys) and, unless `--extra none`,
+    the other benchmark workloads measured the same way under `"workloads"`."""
     rank, world, local = init_ranks(args.gpus)
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    w = workloads.WORKLOADS[args.workload]
+    line = measure_workload(args.workload, args, rank, world, local, dev, main=True)
+    extras = [] if args.extra in ("", "none") else [x for x in args.extra.split(",") if x]
+    others = {}
+    for name in extras:
+        if name == args.workload or name not in workloads.WORKLOADS:
+            continue
+        w = workloads.WORKLOADS[name]
+        if w.kv_heads % world:
+            continue
+        torch.cuda.empty_cache()
+        r = measure_workload(name, args, rank, world, local, dev, main=False)
+        if rank == 0:
+            others[name] = r
+    if rank != 0:
+        return
+    if others:
+        line["workloads"] = others
+    print(json.dumps(line))
+
+
+def measure_workload(name, args, rank, world, local, dev, main):
+    """One workload on this rank's shard: K timed steps (device resident, CUDA
+    events, max over ranks), the scan kernel's own time, the end-to-end call
+    with host buffers, parity against the CPU oracle.  Returns the JSON keys
+    (rank 0; other ranks get None)."""
+    from winnow_b200 import _lib
+    from winnow_b200.packed_attention_cuda import (DecodePlan, decode_workspace,
+                                                   packed_decode_attention)
+    import ctypes
+
+    w = workloads.WORKLOADS[name]
     lib = _lib.lib()
     hq = w.q_heads // world
     hkv = w.kv_heads // world
@@ -250,13 +274,17 @@ def run_ours(args):
         exchange_note = "nccl all_gather_into_tensor + permuting copy"
         if args.exchange == "peer":
             from winnow_b200 import tp
+            why = ""
             try:
                 peer = tp.PeerExchange(B, w.q_heads, D, w.dtype, dev)
                 plans[0].run_exchange(peer.descriptor(), dry_run=True)
-                exchange_note = "fused: merge kernel stores to every rank's buffer over NVLink + flag wait"
             except Exception as exc:                        # noqa: BLE001
+                why = f"{type(exc).__name__}: {exc}"
+            if tp._all_ranks_agree(why == "" and peer is not None, dev, None):
+                exchange_note = "fused: merge kernel stores to every rank's buffer over NVLink + flag wait"
+            else:
                 peer = None
-                exchange_note += f" (peer exchange unavailable: {type(exc).__name__}: {exc})"
+                exchange_note += f" (peer exchange unavailable on some rank{': ' + why if why else ''})"
     graphs = None
     if args.graph and peer is None:
         graphs = [pl.graph() for pl in plans]
@@ -307,65 +335,91 @@ def run_ours(args):
                                 check_page_ids=False, out=target, workspace=ws)
         return gather()
 
-    # ---- parity spot check against the oracle (first sequence, rank 0's heads)
+    # ---- parity against the oracle: the first sequence, every head of the FULL
+    # (gathered) output of a step that used layer 0, checked on every rank
     parity = None
-    if rank == 0 and not args.no_check:
+    if not args.no_check:
         from oracle import tq_oracle as orc
+        got = step(0)                                       # layer 0
+        torch.cuda.synchronize()
+        full = got[:1].float().cpu().clone()
         okv = oracle_view(w, handles[0], 1, hkv)
-        ref = orc.tiled_attention(q_full[:1, :hq].float(), okv, scale)
-        got = packed_decode_attention(q_dev[:1].contiguous(), _first_seq(handles[0]), scale,
-                                      check_page_ids=False)
-        parity = float((got.float().cpu() - ref).abs().max())
+        ref_local = orc.tiled_attention(q_full[:1, rank * hq:(rank + 1) * hq].float(), okv, scale)
+        if world > 1:
+            # every rank contributes the oracle rows of its own heads; the gathered
+            # buffer of every rank must match the assembled reference
+            parts = [torch.zeros_like(ref_local) for _ in range(world)]
+            cpu_group = getattr(measure_workload, "_gloo", None)
+            if cpu_group is None:
+                cpu_group = dist.new_group(backend="gloo")
+                measure_workload._gloo = cpu_group
+            dist.all_gather(parts, ref_local.contiguous(), group=cpu_group)
+            ref = torch.cat(parts, dim=1)
+        else:
+            ref = ref_local
+        parity = max_over_ranks(float((full - ref).abs().max()), world, dev)
 
+    steps = args.steps if main else max(args.steps, 100)
     for i in range(args.warmup):
         step(i)
     barrier(world)
     launches0 = lib.wtq_launch_count()
     plans[0].run()
-    launches = (lib.wtq_launch_count() - launches0) * args.steps   # kernels of ours per step x K
+    launches = (lib.wtq_launch_count() - launches0) * steps         # kernels of ours per step x K
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         start.record()
-        for i in range(args.steps):
+        for i in range(steps):
             step(args.warmup + i)
         end.record()
         barrier(world)
+        steady_ms = None
+        if main and steps < 200:
+            # the same measurement over 200 steps (the K above may be a handful)
+            s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s2.record()
+            for i in range(200):
+                step(args.warmup + i)
+            e2.record()
+            barrier(world)
+            steady_ms = max_over_ranks(s2.elapsed_time(e2) / 200, world, dev)
         # second pass: same steps with events around the page-scan kernel only
-        lib.wtq_profile_enable(args.steps + 8)
-        for i in range(args.steps):
+        n_prof = max(steps, 100)
+        lib.wtq_profile_enable(n_prof + 8)
+        for i in range(n_prof):
             direct_step(args.warmup + i)
         torch.cuda.synchronize()
-    import ctypes
     k_ms, k_n = ctypes.c_double(0.0), ctypes.c_int(0)
     lib.wtq_profile_collect(ctypes.byref(k_ms), ctypes.byref(k_n))
     lib.wtq_profile_disable()
-    ms = max_over_ranks(start.elapsed_time(end) / args.steps, world, dev)
+    ms = max_over_ranks(start.elapsed_time(end) / steps, world, dev)
     kernel_us = max_over_ranks(1e3 * k_ms.value / max(k_n.value, 1), world, dev)
 
     # ---- end to end through the public call with host buffers
     for i in range(min(args.warmup, 3)):
         api_step(i)
     barrier(world)
+    e2e_steps = steps if main else min(steps, 50)
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(e2e_steps):
         q_dev.copy_(q_host, non_blocking=True)
         out_host.copy_(api_step(args.warmup + i), non_blocking=True)
         torch.cuda.synchronize()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / args.steps, world, dev)
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps, world, dev)
 
     # ---- fused append of one token per sequence (reported beside the step)
     append_us = time_append(w, pool, handles, rank, world, dev, args)
 
+    # ---- plain streaming read of this rank's pool: the read-only ceiling
+    read_gbs = None
+    if main:                                                 # slowest rank's figure
+        read_gbs = -max_over_ranks(-time_stream_read(lib, pool.k_pages), world, dev)
+
     exchange_ok = True if peer is None else not peer.timed_out()
-    if rank != 0:
-        return
-    peak, peak_kind = measured_peak()
-    alg_total = w.algorithmic_bytes()
-    alg_rank = w.algorithmic_bytes(kv_heads=hkv, q_heads=hq)
-    achieved = alg_rank / (kernel_us * 1e-6) / 1e9
+    exchange_ok = max_over_ranks(0.0 if exchange_ok else 1.0, world, dev) == 0.0
     cpu = None
-    if not args.no_cpu_baseline:
+    if main and rank == 0 and not args.no_cpu_baseline and world == 1:
         seqs = max(1, min(w.batch, args.cpu_seqs))
         okv = oracle_view(w, handles[0], seqs, hkv)
         t = time_cpu_port(q_full[:seqs, :hq].float(), okv, scale, reps=3)
@@ -374,18 +428,36 @@ def run_ours(args):
                "kind": "port",
                "sample": f"oracle tiled_attention, first {seqs} of {w.batch} sequences, "
                          f"{hkv} of {w.kv_heads} kv heads, median of 3, scaled by tokens"}
+    del plans, graphs, pool, handles
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak()
+    alg_total = w.algorithmic_bytes()
+    alg_rank = w.algorithmic_bytes(kv_heads=hkv, q_heads=hq)
+    achieved = alg_rank / (kernel_us * 1e-6) / 1e9
+    ratio, ratio_source = dram_traffic_ratio(w.name, world)
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "frac_of_8tbs_nominal": achieved / NOMINAL_HBM_GBS,
+                "traffic": alg_rank * ratio, "traffic_source": ratio_source, "peak_kind": peak_kind,
+                "kernel": "page-scan kernel of wtq_decode", "kernel_us": kernel_us,
+                "algorithmic_bytes_per_launch": alg_rank}
+    if not main:
+        return {"step_us": ms * 1e3, "steps": steps, "e2e_us": e2e_ms * 1e3, "append_us": append_us,
+                "hbm_gbs": alg_total / (ms * 1e-3) / 1e9, "roofline": roofline,
+                "config": workload_label(w), "layers_rotated": layers,
+                "parity_max_abs_err_vs_oracle": parity,
+                "exchange_completed_without_timeout": exchange_ok}
     line = {
-        "metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": world, "steps": steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{w.name}: B{w.batch} Hq{w.q_heads} Hkv{w.kv_heads} D{w.head_dim} "
-                               f"ctx{w.context or 'ragged'} page{w.page_size} "
-                               f"{w.bits_k}-bit K/{w.bits_v}-bit V, q {str(w.dtype)[6:]}",
+        "config": {"workload": workload_label(w),
                    "parallelism": f"kv-head tp{world}" if world > 1 else "single gpu",
                    "l2": f"steps rotate over {layers} layers of pages "
                          f"({layers * per_layer / 1e6:.0f} MB per GPU) so each step reads from HBM",
                    "num_splits": args.splits or "auto", "exchange": exchange_note,
                    "launch": "cuda graph replay" if args.graph else "pre-marshalled call"},
+        "steady_us_over_200_steps": None if steady_ms is None else steady_ms * 1e3,
         "hbm_gbs": alg_total / (ms * 1e-3) / 1e9,
         "hbm_frac_of_8tbs_nominal": alg_total / (ms * 1e-3) / 1e9 / (NOMINAL_HBM_GBS * world),
         "tokens_per_s": w.batch / (ms * 1e-3),
@@ -394,19 +466,51 @@ def run_ours(args):
                 "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
                 "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": alg_rank * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE,
-                     "traffic_source": "ncu capture of the scan kernel on config2 (dram read + write "
-                                       "145.5 MB per launch for 138.7 MB algorithmic), scaled by "
-                                       "algorithmic bytes", "peak_kind": peak_kind,
-                     "kernel": "page-scan kernel of wtq_decode", "kernel_us": kernel_us,
-                     "algorithmic_bytes_per_launch": alg_rank},
+        "roofline": roofline,
+        "read_only_gbs": read_gbs,
         "cpu_baseline": cpu,
         "clocks": clocks.summary(),
         "parity_max_abs_err_vs_oracle": parity,
         "exchange_completed_without_timeout": exchange_ok,
     }
-    print(json.dumps(line))
+    return line
+
+
+def workload_label(w) -> str:
+    return (f"{w.name}: B{w.batch} Hq{w.q_heads} Hkv{w.kv_heads} D{w.head_dim} "
+            f"ctx{w.context or 'ragged'} page{w.page_size} "
+            f"{w.bits_k}-bit K/{w.bits_v}-bit V, q {str(w.dtype)[6:]}")
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the scan kernel
+# over its algorithmic bytes, from ncu captures of the named workloads (their
+# summaries are kept under profiles/; the excess over 1 is the chunk states the
+# kernel writes).  Other workloads and shards are scaled with the nearest entry.
+DRAM_TRAFFIC_RATIO = {("config2", 1): 145.5 / 138.7}
+
+
+def dram_traffic_ratio(name: str, world: int):
+    if (name, world) in DRAM_TRAFFIC_RATIO:
+        return DRAM_TRAFFIC_RATIO[(name, world)], f"ncu capture of the scan kernel on {name}, {world} GPU(s)"
+    return DRAM_TRAFFIC_RATIO[("config2", 1)], ("scaled: ratio of an ncu capture on config2, 1 GPU "
+                                               "(not captured for this workload/shard)")
+
+
+def time_stream_read(lib, tensor) -> float:
+    """GB/s of a plain streaming read (wtq_probe_read) over `tensor`'s storage."""
+    flat = tensor.reshape(-1)
+    nbytes = flat.numel() * flat.element_size() // 16 * 16
+    sink = torch.zeros(1, dtype=torch.int32, device=tensor.device)
+    stream = torch.cuda.current_stream(tensor.device).cuda_stream
+    for _ in range(3):
+        lib.wtq_probe_read(flat.data_ptr(), nbytes, sink.data_ptr(), stream)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(10):
+        lib.wtq_probe_read(flat.data_ptr(), nbytes, sink.data_ptr(), stream)
+    e.record()
+    torch.cuda.synchronize()
+    return nbytes * 10 / (s.elapsed_time(e) * 1e-3) / 1e9
 
 
 def _first_seq(handle):
@@ -502,6 +606,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config2", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--extra", default="headline32k,config3,config4,config5",
+                    help="comma list of further workloads reported under \"workloads\" (or none)")
     ap.add_argument("--layers", type=int, default=0, help="layers of pages to rotate over (0=auto)")
     ap.add_argument("--splits", type=int, default=0, help="split-K factor (0 = library's choice)")
     ap.add_argument("--cpu-seqs", type=int, default=2)

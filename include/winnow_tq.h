@@ -165,6 +165,12 @@ int wtq_decode_exchange(const void *q, int dtype, const int64_t q_strides[2],
                         const int32_t *seq_lens, float scale, int B, int Hq, int Hkv, int D, int S,
                         int P, int max_pages, int num_splits, void *workspace,
                         size_t workspace_bytes, int32_t *status, void *stream);
+/* 1 when wtq_decode_exchange has its fused epilogue for these descriptors (the
+ * test the call applies: shape, widths, alignment of pointers and strides, the
+ * WTQ_FORCE_GENERIC switch), 0 when the caller should gather with NCCL.
+ * `workspace`: the buffer the call will be given.  Launches nothing. */
+int wtq_decode_exchange_supported(const wtq_side_t *k_side, const wtq_side_t *v_side, int Hq,
+                                  int Hkv, int D, int S, const void *workspace);
 int wtq_exchange_wait(const uint32_t *local_flags, int world, const uint32_t *step_counter,
                       int64_t spin_limit, int32_t *status, void *stream);
 
@@ -178,7 +184,10 @@ int wtq_exchange_wait(const uint32_t *local_flags, int world, const uint32_t *st
  * (wtq_decode_workspace_bytes for the chosen num_splits) exceeds
  * wtq_decode_static_capacity() are refused with WTQ_ERR_WORKSPACE.  The first
  * call on each device looks the array's device address up (with that device
- * current); make that first call before any stream capture begins.  All calls
+ * current); that is also when the CUDA runtime, which loads modules lazily,
+ * places the array in that device's memory.  Make that first call at start-up,
+ * before any stream capture begins; later calls leave the device's free memory
+ * unchanged.  All calls
  * on a device share the one array: calls that can overlap on the GPU (two
  * streams, two threads) race and must be serialised by the caller.  Nothing
  * here calls cudaMalloc, cudaFree or any allocating routine. */
@@ -213,6 +222,12 @@ int wtq_profile_collect(double *total_ms, int *launches);
  * (query rotation), the scan, scan end to last launch's end (merge). */
 int wtq_profile_phases(double *before_scan_ms, double *scan_ms, double *after_scan_ms, int *calls);
 int wtq_profile_disable(void);
+
+/* Plain streaming read of `bytes` bytes of device memory (16-byte loads, every
+ * byte once), for calibrating the read-only HBM ceiling beside the scan's
+ * numbers; `sink` (optional device word) only keeps the loads alive.  Same role
+ * as the reference study's streaming control (experiments/c27/controls.cu:15-36). */
+int wtq_probe_read(const void *src, size_t bytes, uint32_t *sink, void *stream);
 
 #ifdef __cplusplus
 }

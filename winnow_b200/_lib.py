@@ -13,6 +13,7 @@ from ._build import LIB
 WTQ_F32, WTQ_F16, WTQ_BF16 = 0, 1, 2
 ORDER_AUTO, ORDER_SEQUENTIAL, ORDER_INTERLEAVED16 = -1, 0, 1
 STATUS_BAD_PAGE, STATUS_BAD_POSITION = 1, 2
+STATUS_LAYOUT, STATUS_SCAN_TIMEOUT = 8, 16
 
 _DTYPES = {torch.float32: WTQ_F32, torch.float16: WTQ_F16, torch.bfloat16: WTQ_BF16}
 
@@ -68,6 +69,9 @@ _SIGNATURES = {
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                     c_size_t, c_void_p, c_void_p]),
     "wtq_exchange_wait": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "wtq_decode_exchange_supported": (c_int, [ctypes.POINTER(Side), ctypes.POINTER(Side), c_int, c_int,
+                                              c_int, c_int, c_void_p]),
+    "wtq_probe_read": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p]),
     "wtq_decode_static_capacity": (c_size_t, []),
     "wtq_decode_static": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p,
                                   ctypes.POINTER(c_int64), ctypes.POINTER(Side),

@@ -286,3 +286,56 @@ extern "C" int wtq_exchange_wait(const uint32_t *local_flags, int world,
   return launch_exchange_wait(local_flags, world, step_counter, spin_limit, status,
                               (cudaStream_t)stream);
 }
+
+// ---- measurement aids ---------------------------------------------------------
+// Plain streaming read of `bytes` bytes (16-byte loads, grid-stride, every byte
+// once): the read-only HBM ceiling that the page scan is compared with beside
+// the copy bandwidth.  Same role as the streaming control of the reference's
+// kernel study (experiments/c27/controls.cu:15-36).
+namespace {
+__global__ void __launch_bounds__(256) stream_read_kernel(const uint4 *src, size_t n16,
+                                                          uint32_t *sink) {
+  uint32_t x = 0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {          // four loads in flight per thread
+    const uint4 a = __ldcs(src + i), b = __ldcs(src + i + stride);
+    const uint4 c = __ldcs(src + i + 2 * stride), d = __ldcs(src + i + 3 * stride);
+    x ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w ^ c.x ^ c.y ^ c.z ^ c.w ^ d.x ^ d.y ^ d.z ^ d.w;
+  }
+  for (; i < n16; i += stride) {
+    const uint4 a = __ldcs(src + i);
+    x ^= a.x ^ a.y ^ a.z ^ a.w;
+  }
+  if (x == 0x9e3779b9u && sink != nullptr) atomicXor(sink, x);   // keeps the loads alive
+}
+}  // namespace
+
+extern "C" int wtq_probe_read(const void *src, size_t bytes, uint32_t *sink, void *stream) {
+  if (!src || ((uintptr_t)src & 15) || bytes < 16)
+    return fail(WTQ_ERR_ARG, "wtq_probe_read: need a 16-byte aligned buffer of at least 16 bytes");
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
+  stream_read_kernel<<<sms * 8, 256, 0, (cudaStream_t)stream>>>((const uint4 *)src, bytes / 16, sink);
+  note_launches(1);
+  return check_cuda(cudaGetLastError(), "wtq_probe_read launch");
+}
+
+// Whether wtq_decode_exchange has its fused epilogue for these descriptors: the
+// same test the call itself applies (shape, widths, alignment of every pointer
+// and stride, and the environment switch that forces the generic kernels),
+// without launching anything.  1 = yes, 0 = no (gather with NCCL instead).
+extern "C" int wtq_decode_exchange_supported(const wtq_side_t *k_side, const wtq_side_t *v_side,
+                                             int Hq, int Hkv, int D, int S,
+                                             const void *workspace) {
+  if (!k_side || !v_side || Hkv < 1 || Hq < 1 || Hq % Hkv || !workspace) return 0;
+  DecodeParams p = {};
+  fill_side(p.k, *k_side, D);
+  fill_side(p.v, *v_side, D);
+  p.D = D; p.S = S; p.n_rep = Hq / Hkv;
+  p.q_rot = (const float *)workspace; p.part_acc = (float *)workspace;
+  p.lut = (const uint32_t *)workspace;
+  return mma_eligible(p) && !force_generic() ? 1 : 0;
+}

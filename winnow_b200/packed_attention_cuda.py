@@ -122,12 +122,10 @@ class DecodePlan:
         epilogue (raises `BackendError` if not) without launching anything."""
         a = self._args
         if dry_run:
-            probe = _lib.lib().wtq_decode_auto_splits(a[11], a[12], a[13], a[14], a[17], a[15],
-                                                      self._k_side.bw, self._v_side.bw)
-            eligible = (a[14] == 128 and (self._k_side.bw, self._v_side.bw) in
-                        ((4, 4), (4, 6), (6, 6), (8, 8)) and a[12] // a[13] <= 8
-                        and a[15] >= 16 and a[15] & (a[15] - 1) == 0 and probe >= 1)
-            if not eligible:
+            ok = _lib.lib().wtq_decode_exchange_supported(
+                ctypes.byref(self._k_side), ctypes.byref(self._v_side), a[12], a[13], a[14], a[15],
+                a[19])
+            if not ok:
                 raise _lib.BackendError("no fused exchange epilogue for this shape")
             return None
         stream = torch.cuda.current_stream(self.device).cuda_stream
