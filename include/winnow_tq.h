@@ -137,18 +137,25 @@ int wtq_decode(const void *q, int dtype, const int64_t q_strides[2], void *out,
  * local (B, Hq, D) result, the merge kernel stores this rank's rows straight
  * into EVERY rank's full (B, world*Hq, D) buffer at head offset
  * `head_offset`, through peer-mapped pointers (plain stores over NVLink; no
- * multicast), then publishes `step` in slot `rank` of every rank's flag array.
- * wtq_exchange_wait, enqueued after it, returns once all `world` slots of the
- * local flag array have reached `step`, i.e. the local full buffer is complete.
- * Waits are bounded: after `spin_limit` polls of a slot the kernel gives up,
- * sets WTQ_STATUS_EXCHANGE_TIMEOUT in `status` and returns.  The step number
- * lives in device memory (`step_counter`, zero at start, incremented by every
- * call), so the call's arguments never change and it can be replayed from a
- * CUDA graph; call number s (1, 2, ...) uses buffer set s & 1: the full buffers
- * alternate between two sets because a peer may already be writing step s+1
- * while this rank still reads step s.
+ * multicast); when the last merge block has fenced its stores, one arrival is
+ * added to slot `rank` of every rank's flag array, so a rank's rows of call
+ * number s are complete in a buffer once that slot has reached s x (arrivals
+ * per call).  wtq_exchange_wait, enqueued after it, returns once all `world` slots
+ * of the local flag array have got there, i.e. the local full buffer is
+ * complete.  Waits are bounded: after `spin_limit` polls of a slot the kernel
+ * gives up, sets WTQ_STATUS_EXCHANGE_TIMEOUT in `status` and returns; the buffer
+ * then still holds the late rank's previous rows, so the result is valid only
+ * while that bit is clear.  The bookkeeping lives in device memory
+ * (`step_counter`: FOUR uint32 words, zero at start: calls completed, waits
+ * completed, arrivals per call, spare), so the arguments never change and
+ * the pair of calls can be replayed from a CUDA graph; call number s (1, 2, ...)
+ * uses buffer set s & 1: the full buffers alternate between two sets because a
+ * peer may already be writing step s+1 while this rank still reads step s.
+ * Every rank must make the same sequence of calls with the same shapes (they
+ * then launch the same number of merge blocks).
  * Only the tensor-core path (head_dim 128, widths 4/4, 4/6, 6/6, 8/8) has this
- * epilogue; other shapes get WTQ_ERR_UNSUPPORTED and should gather with NCCL. */
+ * epilogue; other shapes get WTQ_ERR_UNSUPPORTED and should gather with NCCL
+ * (wtq_decode_exchange_supported answers ahead of time). */
 #define WTQ_STATUS_EXCHANGE_TIMEOUT 4
 typedef struct {
   void *const *peer_out[2];       /* DEVICE arrays [world]: every rank's full buffer, sets 0 and 1 */
@@ -156,7 +163,7 @@ typedef struct {
   int64_t out_strides[2];         /* element strides {batch, head} of the full buffers */
   int rank, world;
   int head_offset;                /* first head of the full buffer this rank writes */
-  uint32_t *step_counter;         /* local device uint32: calls completed so far */
+  uint32_t *step_counter;         /* local device uint32[4]: see above */
   uint32_t *done_counter;         /* local device uint32, zero between calls */
 } wtq_exchange_t;
 int wtq_decode_exchange(const void *q, int dtype, const int64_t q_strides[2],
@@ -171,7 +178,7 @@ int wtq_decode_exchange(const void *q, int dtype, const int64_t q_strides[2],
  * `workspace`: the buffer the call will be given.  Launches nothing. */
 int wtq_decode_exchange_supported(const wtq_side_t *k_side, const wtq_side_t *v_side, int Hq,
                                   int Hkv, int D, int S, const void *workspace);
-int wtq_exchange_wait(const uint32_t *local_flags, int world, const uint32_t *step_counter,
+int wtq_exchange_wait(const uint32_t *local_flags, int world, uint32_t *step_counter,
                       int64_t spin_limit, int32_t *status, void *stream);
 
 /* wtq_decode without a caller-supplied workspace.  It has no counterpart in the

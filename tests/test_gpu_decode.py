@@ -356,7 +356,7 @@ def test_exchange_epilogue_with_two_ranks_on_one_gpu(name):
         ex.peer_flags = peer_flags.data_ptr()
         ex.out_strides[0], ex.out_strides[1] = bufs[0][0].stride(0), bufs[0][0].stride(1)
         ex.rank, ex.world, ex.head_offset = rank, world, rank * hq
-        step = torch.zeros(1, dtype=torch.int32, device=dev)
+        step = torch.zeros(4, dtype=torch.int32, device=dev)     # calls, waits, blocks per call
         done = torch.zeros(1, dtype=torch.int32, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         ex.step_counter, ex.done_counter = step.data_ptr(), done.data_ptr()
@@ -374,8 +374,9 @@ def test_exchange_epilogue_with_two_ranks_on_one_gpu(name):
         ref = orc.tiled_attention(qi, okv, scale)
         for rank, (plan, ex, step, done, status, *_r) in enumerate(ranks):
             assert int(status.item()) == 0
-            assert int(step.item()) == call and int(done.item()) == 0
-            assert flags[rank].tolist() == [call] * world
+            calls, waits, blocks = step.tolist()[:3]
+            assert calls == call and waits == call and blocks == 1 and int(done.item()) == 0
+            assert flags[rank].tolist() == [call * blocks] * world
             assert_attention_close(bufs[rank][call & 1].float().cpu(), ref)
 
 
@@ -416,39 +417,40 @@ def test_reference_operator_names_on_the_gpu(name, Q):
 
 def test_exchange_wait_gives_up_and_says_so():
     """The bounded wait of the output exchange, made to run out on purpose: the
-    flags are one step behind (nothing will ever set them), the poll limit is
-    small, so the kernel must return, set WTQ_STATUS_EXCHANGE_TIMEOUT and leave
-    the device usable; with the flags set a second wait reports nothing."""
+    arrival counts are short of what the call waits for (nothing will ever add
+    to them), the poll limit is small, so the kernel must return, set
+    WTQ_STATUS_EXCHANGE_TIMEOUT and leave the device usable; with the counts in
+    place a later wait reports nothing."""
     lib = _lib.lib()
     dev = torch.device("cuda", 0)
-    world = 2
+    world, blocks = 2, 3
     flags = torch.zeros(world, dtype=torch.int32, device=dev)
-    step = torch.ones(1, dtype=torch.int32, device=dev)          # the step being waited for
+    state = torch.tensor([0, 0, blocks, 0], dtype=torch.int32, device=dev)   # calls, waits, blocks
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
-    _lib.check(lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 8,
-                                     status.data_ptr(), stream))
-    torch.cuda.synchronize()
-    assert int(status.item()) & _lib.STATUS_EXCHANGE_TIMEOUT
-    # one rank arrived, the other did not: still a timeout
-    status.zero_()
-    flags[0] = 1
-    _lib.check(lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 8,
-                                     status.data_ptr(), stream))
-    torch.cuda.synchronize()
-    assert int(status.item()) & _lib.STATUS_EXCHANGE_TIMEOUT
-    # everybody arrived: nothing to report, and the context still works
-    status.zero_()
-    flags.fill_(1)
-    _lib.check(lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 8,
-                                     status.data_ptr(), stream))
-    torch.cuda.synchronize()
-    assert int(status.item()) == 0
-    assert float((torch.ones(4, device=dev) * 2).sum().item()) == 8.0
+
+    def wait():
+        status.zero_()
+        _lib.check(lib.wtq_exchange_wait(flags.data_ptr(), world, state.data_ptr(), 8,
+                                         status.data_ptr(), stream))
+        torch.cuda.synchronize()
+        return int(status.item())
+
+    assert wait() & _lib.STATUS_EXCHANGE_TIMEOUT            # wait 1: nobody arrived
+    flags[0] = 2 * blocks                                    # wait 2: one rank complete, one short
+    flags[1] = 2 * blocks - 1
+    assert wait() & _lib.STATUS_EXCHANGE_TIMEOUT
+    flags.fill_(3 * blocks)                                  # wait 3: everybody arrived
+    assert wait() == 0
+    assert state.tolist()[1] == 3
+    assert float((torch.ones(4, device=dev) * 2).sum().item()) == 8.0   # the context still works
+    # the merge blocks of the local call not recorded yet: that is "not arrived" too
+    state[2] = 0
+    assert wait() & _lib.STATUS_EXCHANGE_TIMEOUT
     # malformed calls are refused before any launch
-    assert lib.wtq_exchange_wait(flags.data_ptr(), world, step.data_ptr(), 0, status.data_ptr(),
+    assert lib.wtq_exchange_wait(flags.data_ptr(), world, state.data_ptr(), 0, status.data_ptr(),
                                  stream) != 0
-    assert lib.wtq_exchange_wait(None, world, step.data_ptr(), 8, status.data_ptr(), stream) != 0
+    assert lib.wtq_exchange_wait(None, world, state.data_ptr(), 8, status.data_ptr(), stream) != 0
 
 
 # Seeded wrong implementations of the operator (the reference keeps the same

@@ -278,9 +278,8 @@ extern "C" int wtq_decode_exchange(const void *q, int dtype, const int64_t q_str
                        max_pages, num_splits, workspace, workspace_bytes, status, stream);
 }
 
-extern "C" int wtq_exchange_wait(const uint32_t *local_flags, int world,
-                                 const uint32_t *step_counter, int64_t spin_limit,
-                                 int32_t *status, void *stream) {
+extern "C" int wtq_exchange_wait(const uint32_t *local_flags, int world, uint32_t *step_counter,
+                                 int64_t spin_limit, int32_t *status, void *stream) {
   if (!local_flags || !step_counter || world < 1 || world > 32 || spin_limit < 1)
     return fail(WTQ_ERR_ARG, "wtq_exchange_wait: need flags, 1 <= world <= 32, spin_limit >= 1");
   return launch_exchange_wait(local_flags, world, step_counter, spin_limit, status,

@@ -852,6 +852,31 @@ decode_mma_kernel(DecodeParams p, int chunk_tokens) {
   cp_async_wait<0>();
 }
 
+// End of a merge block in the exchange form.  The block's rows are on their way
+// to every rank's buffer; after a barrier (which makes the block's stores
+// visible to thread 0) and a system-scope fence (which orders them before what
+// follows), thread 0 counts the block on a local counter.  The last block to
+// arrive has, through that counter, seen every other block's fence; it fences
+// once more and adds ONE arrival to slot `rank` of every rank's flag array
+// (one remote operation per peer and call: an arrival per block, measured on
+// two GPUs, cost 5 us more).  A rank's rows of call number s are complete in a
+// buffer when that slot has reached s x state[2] (arrivals per call, 1 here).
+// The last block also advances the call counter (state[0]).
+__device__ __forceinline__ void publish_rows(const MergeParams &p, uint32_t step, unsigned blocks) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(p.done_counter, 1u) == blocks - 1) {
+      *p.done_counter = 0;
+      p.step_counter[2] = 1u;
+      p.step_counter[0] = step;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r)
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.peer_flags[r] + p.rank) : "memory");
+    }
+  }
+}
+
 // Merge of the chunk states of `hpb` query heads of one (sequence, kv head)
 // group and rotation of their output rows back to the model basis:
 // out = (sum_c w_c acc_c / sum_c w_c l_c) Pi_V with w_c = 2^(m_c - max m).  Only
@@ -1055,24 +1080,7 @@ __global__ void __launch_bounds__(kMergeThreads, 1) merge_group_kernel(
   }
   __syncthreads();                        // shared arrays are reused by the next group
   }
-  if (p.world > 0) {
-    // Publish: every block fences its peer stores and counts itself; the last
-    // one to arrive writes this rank's step into every rank's flag array.
-    // (the barrier makes the block's stores visible to thread 0, whose fence
-    // then orders them, cumulatively, before its arrival on the counter)
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence_system();
-      const unsigned blocks = gridDim.x * gridDim.y;
-      if (atomicAdd(p.done_counter, 1u) == blocks - 1) {
-        *p.done_counter = 0;
-        *p.step_counter = exchange_step;
-        __threadfence_system();
-        for (int r = 0; r < p.world; ++r)
-          *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = exchange_step;
-      }
-    }
-  }
+  if (p.world > 0) publish_rows(p, exchange_step, gridDim.x * gridDim.y);
 }
 
 // The same merge with many small blocks: one 128-thread block per `hpb` query
@@ -1169,45 +1177,40 @@ __global__ void __launch_bounds__(128, 8) merge_small_kernel(MergeParams p, cons
       }
     }
   }
-  if (p.world > 0) {                      // publish, as in merge_group_kernel
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence_system();
-      if (atomicAdd(p.done_counter, 1u) == gridDim.x * gridDim.y - 1) {
-        *p.done_counter = 0;
-        *p.step_counter = exchange_step;
-        __threadfence_system();
-        for (int r = 0; r < p.world; ++r)
-          *reinterpret_cast<volatile uint32_t *>(p.peer_flags[r] + p.rank) = exchange_step;
-      }
-    }
-  }
+  if (p.world > 0) publish_rows(p, exchange_step, gridDim.x * gridDim.y);
 }
 
-// Waits (bounded) until every slot of the local flag array has reached `step`.
-__global__ void exchange_wait_kernel(const uint32_t *flags, int world, const uint32_t *step_counter,
+// Waits (bounded) until every rank's rows of the call being waited for are in
+// the local buffer: slot r of the local flag array counts the arrivals of rank
+// r's merge blocks, `state` = {calls completed, waits completed, merge blocks
+// per call}.  The kernel numbers its own calls (state[1]), so it does not
+// depend on the merge kernel ahead of it and starts polling as soon as it is
+// scheduled; the blocks per call are read inside the loop because the local
+// merge may not have recorded them yet.
+__global__ void exchange_wait_kernel(const uint32_t *flags, int world, uint32_t *state,
                                      long long spin_limit, int32_t *status) {
   const int r = threadIdx.x;
-  // launched early (programmatic dependent launch): wait for the merge kernel
-  // ahead of this one, which advances the step counter
-  asm volatile("griddepcontrol.wait;\n" ::: "memory");
-  const uint32_t step = *reinterpret_cast<const volatile uint32_t *>(step_counter);
+  uint32_t step = 0;
+  if (r == 0) step = ++state[1];
+  step = __shfl_sync(0xffffffffu, step, 0);
   if (r < world) {
     const volatile uint32_t *slot = flags + r;
+    const volatile uint32_t *blocks = state + 2;
     bool arrived = false;
     for (long long i = 0; i < spin_limit; ++i) {
-      if ((int32_t)(*slot - step) >= 0) {
+      const uint32_t n = *blocks;
+      if (n != 0u && (int32_t)(*slot - step * n) >= 0) {
         arrived = true;
         break;
       }
-      __nanosleep(100);
+      __nanosleep(20);
     }
     if (!arrived && status != nullptr) atomicOr(status, WTQ_STATUS_EXCHANGE_TIMEOUT);
   }
   __threadfence_system();
 }
 
-int launch_exchange_wait(const uint32_t *flags, int world, const uint32_t *step_counter,
+int launch_exchange_wait(const uint32_t *flags, int world, uint32_t *state,
                          long long spin_limit, int32_t *status, cudaStream_t stream) {
   cudaLaunchAttribute pdl;
   pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1218,8 +1221,8 @@ int launch_exchange_wait(const uint32_t *flags, int world, const uint32_t *step_
   cfg.stream = stream;
   cfg.attrs = &pdl;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, exchange_wait_kernel, flags, world, step_counter,
-                                     spin_limit, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, exchange_wait_kernel, flags, world, state, spin_limit,
+                                     status);
   note_launches(1);
   return check_cuda(e, "wtq_exchange_wait launch");
 }

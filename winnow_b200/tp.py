@@ -106,7 +106,7 @@ class PeerExchange:
                      .view(batch, q_heads, 1, head_dim) for i in range(2)]
         self.flags = self._buf[2 * out_bytes: 2 * out_bytes + 4 * self.world].view(torch.int32)
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.step_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.step_dev = torch.zeros(4, dtype=torch.int32, device=dev)   # calls, waits, blocks per call
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.step = 0
         self.device = dev
