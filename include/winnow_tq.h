@@ -205,6 +205,22 @@ int wtq_decode_static(const void *q, int dtype, const int64_t q_strides[2], void
                       const int32_t *seq_lens, float scale, int B, int Hq, int Hkv, int D, int S,
                       int P, int max_pages, int num_splits, int32_t *status, void *stream);
 
+/* Replaces dense_decode_attention (turboquant_kv/packed_attention_triton.py:190-201),
+ * the matched unquantised arm of the decode operator: the same split-K schedule
+ * over the same page table, on pages (P, Hkv, S, D) of `page_dtype` (fp16, bf16
+ * or fp32; the last two dimensions contiguous; k_strides / v_strides = element
+ * strides {page, head}).  q, out as in wtq_decode.  num_splits >= 1 (the
+ * caller's choice; 1 = one block per (kv head, sequence)).  Workspace:
+ * wtq_dense_workspace_bytes. */
+size_t wtq_dense_workspace_bytes(int B, int Hq, int D, int num_splits);
+int wtq_dense_decode(const void *q, int q_dtype, const int64_t q_strides[2], void *out,
+                     const int64_t out_strides[2], const void *k_pages, const void *v_pages,
+                     int page_dtype, const int64_t k_strides[2], const int64_t v_strides[2],
+                     const int32_t *page_table, int64_t table_stride, const int32_t *seq_lens,
+                     float scale, int B, int Hq, int Hkv, int D, int S, int P, int max_pages,
+                     int num_splits, void *workspace, size_t workspace_bytes, int32_t *status,
+                     void *stream);
+
 /* Replaces tq_dequant / tq_dequant_cuda (turboquant_kv/kernel.py:78-115,
  * turboquant_kv/csrc/tq_dequant.cu:186-211): N packed rows -> (N, D) of
  * `out_dtype`.  Logical row r is read from source row (r / L) * MAXLEN + r % L

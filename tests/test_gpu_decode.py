@@ -292,6 +292,117 @@ def test_legacy_contiguous_cache_roundtrip():
         cache.update(torch.zeros(B, H, 64, D, device=DEV), torch.zeros(B, H, 64, D, device=DEV), 1)
 
 
+def test_legacy_cache_outlier_channels_and_hf_protocol():
+    """The 3.5-bit operating point of the reference's legacy cache
+    (turboquant_kv/cache.py:183-191,224-233,289-303): 32 outlier channels at 4
+    bits, the other 96 at 3 bits, each part with its own rotation, codebook and
+    norms.  Checked against the oracle's quantizers applied to the same channel
+    split; the classes are `transformers` cache classes and keep the
+    reference's accounting helpers."""
+    from transformers.cache_utils import DynamicCache, DynamicLayer
+    from winnow_b200.cache import TQPackedCache, TQPackedLayer
+    from winnow_b200.native_kernel import existing_native_kernel
+    assert issubclass(TQPackedCache, DynamicCache) and issubclass(TQPackedLayer, DynamicLayer)
+    g = torch.Generator().manual_seed(31)
+    B, H, D, n_out = 2, 2, 128, 32
+    cache = TQPackedCache(D, 3, DEV, max_cache_len=40, num_layers=1,
+                          num_outlier_channels=n_out, outlier_bits=4)
+    boost = torch.ones(D)
+    boost[torch.randperm(D, generator=g)[:n_out]] = 6.0          # clear outlier channels
+    chunks_k, chunks_v = [], []
+    for n in (9, 1):
+        k = (torch.randn(B, H, n, D, generator=g) * boost).to(torch.bfloat16)
+        v = (torch.randn(B, H, n, D, generator=g) * boost).to(torch.bfloat16)
+        chunks_k.append(k), chunks_v.append(v)
+        K, V = cache.update(k.to(DEV), v.to(DEV), 0)
+    layer = cache.layers[0]
+    assert K.shape == (B, H, 10, D) and cache.get_seq_length() == 10
+    assert layer.get_mask_sizes(1) == (10, 0) and layer.get_max_cache_shape() == 40
+    rms = chunks_k[0].float().pow(2).mean(dim=(0, 1, 2)).sqrt()
+    mask = torch.zeros(D, dtype=torch.bool)
+    mask[rms.topk(n_out).indices] = True
+    assert torch.equal(layer._mask.cpu(), mask)
+    reg, out = orc.OracleQuantizer.get(3, D - n_out, 42), orc.OracleQuantizer.get(4, n_out, 43)
+    for chunks, got in ((chunks_k, K), (chunks_v, V)):
+        ref = torch.zeros(B, H, 10, D)
+        at = 0
+        for chunk in chunks:                                    # same call grouping as the updates
+            n = chunk.shape[2]
+            for o, sel, bw, dim in ((reg, ~mask, 3, D - n_out), (out, mask, 4, n_out)):
+                idx, nrm = o.quantize(chunk.float()[..., sel])
+                part = orc.dequantize_rows(orc.pack(idx, bw), nrm.to(torch.float16),
+                                           o.centroids, o.Pi, bw, dim)
+                ref[:, :, at:at + n][..., sel] = part
+            at += n
+        ref = ref.to(torch.bfloat16).float()
+        ulp = (ref.abs() * 2.0 ** -7).clamp(min=1e-30)
+        assert ((got.float().cpu() - ref).abs() <= ulp).all()
+    assert abs(cache.effective_bits() - 3.5) < 1e-9
+    assert cache.persistent_bytes() == 2 * B * H * 40 * (36 + 16 + 4)
+    assert cache.persistent_bytes_used() == cache.persistent_bytes() * 10 // 40
+    assert cache.transient_bytes() == 2 * B * H * 10 * D * 2
+    layer.reset()
+    assert cache.get_seq_length() == 0
+    # the reference's adapter name for its native kernel resolves to wtq_dequant
+    fn = existing_native_kernel()
+    tq = _get_quantizer(4, 128, DEV, 42)
+    packed = torch.randint(0, 256, (5, 64), dtype=torch.uint8, generator=g).to(DEV)
+    norms = torch.rand(5, generator=g).half().to(DEV)
+    a = fn(packed, norms, tq.centroids, tq.Pi, 4, 128, out=torch.empty(5, 128, device=DEV))
+    b = dequantize_rows(packed, norms, tq.centroids, tq.Pi, 4, 128, out=torch.empty(5, 128, device=DEV))
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("splits", [1, 3, 0])
+def test_dense_page_arm_matches_sdpa(dtype, splits):
+    """The unquantised paged arm (reference: turboquant_kv/test_packed_attention_triton.py:
+    153-173): same page table walk, no codebook; against fp32 attention over the
+    gathered history.  Also through the attention-interface entry point, under
+    its own backend name and the reference's alias."""
+    from winnow_b200.packed_attention_cuda import dense_decode_attention
+    g = torch.Generator().manual_seed(9)
+    B, Hq, Hkv, D, S = 3, 28, 4, 128, 16
+    lens = (70, 0, 33)
+    pages_n = sum(-(-L // S) for L in lens) + 2
+    order = torch.randperm(pages_n, generator=g)
+    kp = torch.randn(pages_n, Hkv, S, D, generator=g).to(dtype)
+    vp = torch.randn(pages_n, Hkv, S, D, generator=g).to(dtype)
+    table = torch.full((B, 6), -1, dtype=torch.int32)
+    at = 0
+    for b, L in enumerate(lens):
+        n = -(-L // S)
+        table[b, :n] = order[at:at + n].to(torch.int32)
+        at += n
+    q = (torch.randn(B, Hq, 1, D, generator=g) * 0.3).to(dtype)
+    scale = D ** -0.5
+    ref = torch.zeros(B, Hq, 1, D)
+    for b, L in enumerate(lens):
+        if L == 0:
+            continue
+        ids = table[b, : -(-L // S)].long()
+        k = kp[ids].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :L].float().repeat_interleave(Hq // Hkv, 0)
+        v = vp[ids].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :L].float().repeat_interleave(Hq // Hkv, 0)
+        w = torch.softmax((q[b].float() @ k.transpose(1, 2)) * scale, dim=-1)
+        ref[b] = w @ v
+    kv = pa.DenseKV(kp.to(DEV), vp.to(DEV), table.to(DEV),
+                    torch.tensor(lens, dtype=torch.int32, device=DEV), D)
+    got = dense_decode_attention(q.to(DEV), kv, scale, num_splits=splits)
+    assert got.dtype == dtype and got.shape == q.shape
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-3
+    assert (got.float().cpu() - ref).abs().max() < tol
+    assert (got[1] == 0).all()
+    pb.BACKEND_COUNTS.clear()
+    out, _ = pb.winnow_packed_attention(None, q.to(DEV), kv, kv, None, scaling=scale)
+    assert pb.BACKEND_COUNTS["cuda_dense"] == 1
+    assert (out.transpose(1, 2).float().cpu() - ref).abs().max() < tol
+    kv.decode_backend = "triton_dense"
+    pb.winnow_packed_attention(None, q.to(DEV), kv, kv, None, scaling=scale)
+    assert pb.BACKEND_COUNTS["cuda_dense"] == 2 and pb.BACKEND_COUNTS["triton_dense"] == 1
+    with pytest.raises(pa.UnsupportedLayout):
+        dense_decode_attention(q.repeat(1, 1, 2, 1).to(DEV), kv, scale)
+
+
 def test_more_sequences_than_the_shared_prefix_holds():
     """1100 short ragged sequences: the chunk prefix no longer fits the kernel's
     shared-memory copy, so the work queue reads the one in the workspace."""

@@ -78,6 +78,12 @@ _SIGNATURES = {
                                   ctypes.POINTER(Side), c_void_p, c_int64, c_void_p, c_float,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                   c_void_p]),
+    "wtq_dense_workspace_bytes": (c_size_t, [c_int] * 4),
+    "wtq_dense_decode": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p,
+                                 ctypes.POINTER(c_int64), c_void_p, c_void_p, c_int,
+                                 ctypes.POINTER(c_int64), ctypes.POINTER(c_int64), c_void_p, c_int64,
+                                 c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "wtq_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int64, c_int64, c_int64, c_void_p]),
 }

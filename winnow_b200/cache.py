@@ -167,29 +167,59 @@ def _get_quantizer(bw, dim, dev, seed=42) -> TurboQuantMSE:
     return _QUANTIZER_CACHE[key]
 
 
-class TQPackedLayer:
+try:                                      # the legacy cache is an HF cache when transformers is present
+    from transformers.cache_utils import DynamicCache as _CacheBase, DynamicLayer as _LayerBase
+except Exception:                         # noqa: BLE001 - optional dependency
+    _CacheBase = _LayerBase = object
+
+
+class TQPackedLayer(_LayerBase):
     """Contiguous packed KV of one layer: a preallocated (B, H, max_len, NB) ring
     of codes plus fp16 norms, written in place, and a transient dequantization
-    of the whole history per step (reference: turboquant_kv/cache.py:154-330).
+    of the whole history per step (reference: turboquant_kv/cache.py:154-373).
+    A `transformers` `DynamicLayer` when that package is importable, as the
+    reference's class is, so it can sit in a `past_key_values` cache.
 
     This is the legacy cache of the reference: it hands dense K, V to stock
     attention, so its decode cost grows with the history.  The paged cache with
     compressed-domain attention (packed_backend.PagedPackedCache) is the path
     to use; this class exists for callers that still hold the old interface.
     Both directions run on the GPU: `wtq_quantize` with fused packing for the
-    write, `wtq_dequant` reading the ring in place for the read.  The outlier
-    channel variant of the reference (two quantizers over a channel mask) is
-    not provided.
+    write, `wtq_dequant` reading the ring in place for the read.
+
+    Outlier channels (turboquant_kv/cache.py:183-191,224-233,289-303): with
+    `num_outlier_channels` > 0 and `outlier_bits` > `bit_width`, the channels
+    with the largest RMS in the first keys seen go to a second quantizer
+    (`outlier_bits` wide, rotation seed 43) over just those channels, the rest
+    to the regular one over the remaining channels; each part has its own codes
+    and norms, and the read scatters the two reconstructions back into place.
+    The keyword arguments that chose among the reference's dequantization
+    back-ends (`chunk`, `use_kernel`, `allow_tf32`, `kernel_backend`,
+    `native_kernel`) are accepted and ignored: there is one back-end here.
     """
 
     def __init__(self, head_dim: int, bit_width: int, device, max_cache_len: int,
-                 num_outlier_channels: int = 0, outlier_bits: int = 0, **_ignored):
-        if num_outlier_channels > 0 and outlier_bits > bit_width:
-            raise NotImplementedError("outlier channels are not supported by the CUDA backend")
+                 num_outlier_channels: int = 0, outlier_bits: int = 0, chunk: int = 1024,
+                 use_kernel: bool = True, allow_tf32: bool = True, kernel_backend: str = "auto",
+                 native_kernel=None, dispatcher=None):
+        if _LayerBase is not object:
+            super().__init__()
+        del chunk, use_kernel, allow_tf32, native_kernel
+        if kernel_backend not in {"auto", "torch_fp32", "triton_fp32", "triton_tf32",
+                                  "native_cuda_fp32", "cuda_sm100"}:
+            raise ValueError(f"unknown kernel_backend={kernel_backend!r}")
+        self._dispatcher = dispatcher
         self._bw, self._hd, self._max = bit_width, head_dim, max_cache_len
-        self._tq = _get_quantizer(bit_width, head_dim, device)
-        self._nb = packed_bytes(head_dim, bit_width)
+        split = num_outlier_channels > 0 and outlier_bits > bit_width
+        self._out_dim = num_outlier_channels if split else 0
+        self._reg_dim = head_dim - self._out_dim
+        self._out_bw = outlier_bits
+        self._tq = _get_quantizer(bit_width, self._reg_dim, device)
+        self._tq_out = _get_quantizer(outlier_bits, self._out_dim, device, seed=43) if split else None
+        self._nb = packed_bytes(self._reg_dim, bit_width)
+        self._nb_out = packed_bytes(self._out_dim, outlier_bits) if split else 0
         self._len = 0
+        self._channels = None               # (regular channel ids, outlier channel ids)
         self.is_initialized = False
         self.last_dispatch_decision = None
 
@@ -198,31 +228,56 @@ class TQPackedLayer:
         B, H, _, D = ks.shape
         dev = _lib.require_cuda(ks, vs)
         self.dtype, self.device = ks.dtype, dev
-        self._pk = torch.empty(B, H, self._max, self._nb, dtype=torch.uint8, device=dev)
-        self._pv = torch.empty_like(self._pk)
-        self._nk = torch.empty(B, H, self._max, dtype=torch.float16, device=dev)
-        self._nv = torch.empty_like(self._nk)
+
+        def ring(nb):
+            return torch.empty(B, H, self._max, nb, dtype=torch.uint8, device=dev)
+
+        def norms():
+            return torch.empty(B, H, self._max, dtype=torch.float16, device=dev)
+
+        # per tensor (K, V): [regular codes, regular norms, outlier codes, outlier norms]
+        self._k = [ring(self._nb), norms(), None, None]
+        self._v = [ring(self._nb), norms(), None, None]
+        if self._out_dim:
+            for side in (self._k, self._v):
+                side[2], side[3] = ring(self._nb_out), norms()
+            rms = ks.float().pow(2).mean(dim=(0, 1, 2)).sqrt()
+            top = rms.topk(min(self._out_dim, D)).indices
+            mask = torch.zeros(D, dtype=torch.bool, device=dev)
+            mask[top] = True
+            self._mask = mask
+            self._channels = ((~mask).nonzero().flatten(), mask.nonzero().flatten())
         self._shape = (B, H, D)
-        self.last_dispatch_decision = default_dispatcher().select(
+        self.last_dispatch_decision = (self._dispatcher or default_dispatcher()).select(
             Hardware.from_torch(torch, dev), Shape(B, H, self._max, D, self._bw),
             NumericalContract.quantization_aware())
         if self.last_dispatch_decision.backend == "none":
             raise _lib.BackendError(self.last_dispatch_decision.reason)
         self.is_initialized = True
 
-    def _store(self, x, pos, n, codes, norms):
-        packed, nrm = self._tq.quantize(x, packed=True)
-        codes[:, :, pos:pos + n] = packed
-        norms[:, :, pos:pos + n] = nrm.to(torch.float16)
+    def _store(self, x, pos, n, side):
+        parts = ((self._tq, None, 0),) if not self._out_dim else (
+            (self._tq, self._channels[0], 0), (self._tq_out, self._channels[1], 2))
+        for tq, channels, at in parts:
+            src = x if channels is None else x.float().index_select(-1, channels)
+            packed, nrm = tq.quantize(src, packed=True)
+            side[at][:, :, pos:pos + n] = packed
+            side[at + 1][:, :, pos:pos + n] = nrm.to(torch.float16)
 
-    def _load(self, length, codes, norms):
+    def _load(self, length, side):
         B, H, D = self._shape
         out = torch.empty(B, H, length, D, dtype=self.dtype, device=self.device)
-        return dequantize_rows(codes[:, :, :length], norms[:, :, :length], self._tq.centroids,
-                               self._tq.Pi, self._bw, D, out=out)
-
-    def get_seq_length(self) -> int:
-        return self._len
+        if not self._out_dim:
+            return dequantize_rows(side[0][:, :, :length], side[1][:, :, :length],
+                                   self._tq.centroids, self._tq.Pi, self._bw, D, out=out)
+        for tq, channels, at, bw, dim in ((self._tq, self._channels[0], 0, self._bw, self._reg_dim),
+                                          (self._tq_out, self._channels[1], 2, self._out_bw,
+                                           self._out_dim)):
+            part = torch.empty(B, H, length, dim, dtype=self.dtype, device=self.device)
+            dequantize_rows(side[at][:, :, :length], side[at + 1][:, :, :length], tq.centroids,
+                            tq.Pi, bw, dim, out=part)
+            out.index_copy_(-1, channels, part)
+        return out
 
     @torch.no_grad()
     def update(self, key_states, value_states, *args, **kwargs):
@@ -232,28 +287,95 @@ class TQPackedLayer:
         if self._len + n > self._max:
             raise RuntimeError(f"TQPackedLayer overflow: {self._len}+{n} > max_cache_len="
                                f"{self._max}. Raise max_cache_len.")
-        self._store(key_states, self._len, n, self._pk, self._nk)
-        self._store(value_states, self._len, n, self._pv, self._nv)
+        self._store(key_states, self._len, n, self._k)
+        self._store(value_states, self._len, n, self._v)
         self._len += n
-        return self._load(self._len, self._pk, self._nk), self._load(self._len, self._pv, self._nv)
+        return self._load(self._len, self._k), self._load(self._len, self._v)
 
-    def packed_bytes_held(self) -> int:
-        """Persistent bytes of this layer (codes + norms for the whole ring)."""
+    # ---- cache protocol ----------------------------------------------------------
+    def get_seq_length(self, *args, **kwargs) -> int:
+        return self._len
+
+    def get_mask_sizes(self, query_length: int = 0, *args, **kwargs):
+        return self._len, 0
+
+    def get_max_length(self, *args, **kwargs):
+        return self._max
+
+    def get_max_cache_shape(self, *args, **kwargs):
+        return self._max
+
+    def reset(self):
+        self._len = 0
+
+    # ---- accounting --------------------------------------------------------------
+    def _tensors(self):
+        if not self.is_initialized:
+            return []
+        return [t for side in (self._k, self._v) for t in side if t is not None]
+
+    def persistent_bytes(self) -> int:
+        """Bytes this layer holds between steps (codes + norms for the whole ring)."""
+        return sum(t.numel() * t.element_size() for t in self._tensors())
+
+    packed_bytes_held = persistent_bytes
+
+    def persistent_bytes_used(self) -> int:
+        """The same, counting only the positions written so far."""
+        return int(self.persistent_bytes() * self._len / self._max) if self._max else 0
+
+    def transient_bytes(self) -> int:
+        """Bytes of the dequantized K and V handed to attention this step."""
         if not self.is_initialized:
             return 0
-        return sum(t.numel() * t.element_size() for t in (self._pk, self._pv, self._nk, self._nv))
+        B, H, D = self._shape
+        return 2 * B * H * self._len * D * torch.empty((), dtype=self.dtype).element_size()
 
 
-class TQPackedCache:
-    """A list of `TQPackedLayer`s with the `update(k, v, layer_idx)` protocol."""
+class TQPackedCache(_CacheBase):
+    """`past_key_values` made of `TQPackedLayer`s (reference:
+    turboquant_kv/cache.py:376-419): `TQPackedCache(config, bit_width,
+    max_cache_len, device=...)` as there, or, without a model config,
+    `TQPackedCache(head_dim, bit_width, device, max_cache_len, num_layers)`."""
 
-    def __init__(self, head_dim: int, bit_width: int, device, max_cache_len: int,
-                 num_layers: int, **layer_kwargs):
-        self.layers = [TQPackedLayer(head_dim, bit_width, device, max_cache_len, **layer_kwargs)
+    def __init__(self, config_or_head_dim, bit_width: int, *args, **kwargs):
+        if _CacheBase is not object:
+            super().__init__()
+        if hasattr(config_or_head_dim, "num_hidden_layers"):
+            cfg = config_or_head_dim
+            head_dim = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+            num_layers = cfg.num_hidden_layers
+            max_cache_len = args[0] if args else kwargs.pop("max_cache_len")
+            device = args[1] if len(args) > 1 else kwargs.pop("device", "cuda")
+        else:
+            head_dim = int(config_or_head_dim)
+            device = args[0] if args else kwargs.pop("device")
+            max_cache_len = args[1] if len(args) > 1 else kwargs.pop("max_cache_len")
+            num_layers = args[2] if len(args) > 2 else kwargs.pop("num_layers")
+        self.layers = [TQPackedLayer(head_dim, bit_width, device, max_cache_len, **kwargs)
                        for _ in range(num_layers)]
+        self.bit_width, self.head_dim = bit_width, head_dim
+        self.append_new_layers = lambda *a, **k: None
 
     def update(self, key_states, value_states, layer_idx: int, *args, **kwargs):
         return self.layers[layer_idx].update(key_states, value_states)
 
-    def get_seq_length(self, layer_idx: int = 0) -> int:
+    def get_seq_length(self, layer_idx: int = 0, *args, **kwargs) -> int:
         return self.layers[layer_idx].get_seq_length()
+
+    def persistent_bytes(self) -> int:
+        return sum(layer.persistent_bytes() for layer in self.layers)
+
+    def persistent_bytes_used(self) -> int:
+        return sum(layer.persistent_bytes_used() for layer in self.layers)
+
+    def transient_bytes(self) -> int:
+        return max((layer.transient_bytes() for layer in self.layers), default=0)
+
+    def effective_bits(self) -> float:
+        """Stored bits per KV element, norms included."""
+        layer = self.layers[0]
+        if not layer.is_initialized:
+            return float("nan")
+        bits = 8 * (layer._nb + layer._nb_out) + 16 * (2 if layer._out_dim else 1)
+        return bits / self.head_dim

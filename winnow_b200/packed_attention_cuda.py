@@ -184,6 +184,54 @@ def packed_decode_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
         return plan.run()
 
 
+@torch.no_grad()
+def dense_decode_attention(q: torch.Tensor, kv: "pa.DenseKV", scale: float, *, num_splits: int = 1,
+                           allow_tf32: bool = False, num_warps: int = 4, num_stages: int = 2,
+                           pages_per_iter: int = 1, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Unquantised paged decode with the same split-K schedule: the matched
+    baseline arm (reference: turboquant_kv/packed_attention_triton.py:190-201).
+    q (B, Hq, 1, D) -> (B, Hq, 1, D) in q.dtype; pages (P, Hkv, S, D) in fp16,
+    bf16 or fp32.  `num_splits` <= 0 picks about four blocks per SM.  The
+    Triton tuning keywords are accepted and ignored."""
+    del allow_tf32, num_warps, num_stages, pages_per_iter
+    if q.dim() != 4 or q.shape[2] != 1 or not q.is_cuda:
+        raise pa.UnsupportedLayout("dense kernel: CUDA decode only (one query token per sequence)")
+    B, Hq, _, D = q.shape
+    kp, vp = kv.k_pages, kv.v_pages
+    if (kp.dim() != 4 or kp.shape != vp.shape or kp.dtype != vp.dtype or kp.shape[3] != D
+            or kp.stride(-1) != 1 or kp.stride(-2) != D or vp.stride(-1) != 1 or vp.stride(-2) != D
+            or kp.dtype not in (torch.float32, torch.float16, torch.bfloat16) or D > 256):
+        raise pa.UnsupportedLayout("dense kernel: unsupported page layout")
+    Hkv, S, P = kp.shape[1], kp.shape[2], kp.shape[0]
+    if Hq % Hkv or kv.page_table.dtype != torch.int32 or kv.seq_lens.dtype != torch.int32 \
+            or kv.page_table.shape[0] != B or kv.page_table.stride(-1) != 1:
+        raise pa.UnsupportedLayout("dense kernel: malformed page table, lengths or head counts")
+    dev = _lib.require_cuda(q, kp, vp, kv.page_table, kv.seq_lens)
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    out = torch.empty(B, Hq, 1, D, dtype=q.dtype, device=dev)
+    max_pages = kv.page_table.shape[1]
+    if B == 0 or max_pages == 0:
+        return out.zero_()
+    splits = int(num_splits or 0)
+    if splits <= 0:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        tiles = max(1, -(-max_pages * S // 32))
+        splits = max(1, min(tiles, -(-4 * sms // max(B * Hkv, 1)), 1024))
+    lib = _lib.lib()
+    ws = torch.empty(lib.wtq_dense_workspace_bytes(B, Hq, D, splits), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.wtq_dense_decode(
+            q.data_ptr(), _lib.dtype_code(q.dtype), _lib.i64x(q.stride(0), q.stride(1)),
+            out.data_ptr(), _lib.i64x(out.stride(0), out.stride(1)), kp.data_ptr(), vp.data_ptr(),
+            _lib.dtype_code(kp.dtype), _lib.i64x(kp.stride(0), kp.stride(1)),
+            _lib.i64x(vp.stride(0), vp.stride(1)), kv.page_table.data_ptr(), kv.page_table.stride(0),
+            kv.seq_lens.contiguous().data_ptr(), float(scale), B, Hq, Hkv, D, S, P, max_pages, splits,
+            ws.data_ptr(), ws.numel(), status.data_ptr() if status is not None else None,
+            _lib.stream_ptr(dev)))
+    return out
+
+
 # Serving loops call the operator every step with the same buffers (query and
 # output staging tensors, one layer's pages, the batch's table and lengths,
 # updated in place).  When the caller supplies `out` and `workspace` and has

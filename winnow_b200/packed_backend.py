@@ -29,7 +29,7 @@ import torch.nn.functional as F
 from . import _lib
 from . import packed_attention as pa
 from .cache import _get_quantizer, dequantize_rows
-from .packed_attention_cuda import _side, packed_decode_attention
+from .packed_attention_cuda import _side, dense_decode_attention, packed_decode_attention
 from .packing import packed_bytes
 from .page_pool import PagePool, StalePage
 
@@ -248,8 +248,15 @@ def append_tokens(k, v, k_pages, k_norms, v_pages, v_norms, page_table, seq_lens
 def select_decode_backend(query: torch.Tensor, kv, requested: str) -> str:
     """Which operator serves a decode step.  Unsupported requests fail loudly."""
     if isinstance(kv, pa.DenseKV):
-        if requested in ("auto", "dense_sdpa"):
+        if requested == "dense_sdpa":
             return "dense_sdpa"
+        if requested in ("auto", "cuda_dense", "triton_dense"):
+            if query.is_cuda:
+                _lib.lib()                       # raises if the library is not built
+                return "cuda_dense"
+            if requested == "auto":
+                return "dense_sdpa"
+            raise RuntimeError(f"{requested} requested but the query is not on a CUDA device")
         raise ValueError(f"backend {requested!r} does not read dense pages")
     if requested not in DECODE_BACKENDS:
         raise ValueError(f"unknown decode backend {requested!r}")
@@ -330,7 +337,12 @@ def winnow_packed_attention(module, query, key, value, attention_mask, dropout: 
     if isinstance(key, pa.DenseKV):
         backend = "dense_sdpa" if Q > 1 else select_decode_backend(query, key, requested)
         BACKEND_COUNTS[("prefill_" if Q > 1 else "") + backend] += 1
-        out = _dense_sdpa(query, key, scaling)
+        if Q == 1 and requested == "triton_dense":
+            BACKEND_COUNTS["triton_dense"] += 1            # the reference's name, kept as an alias
+        if backend == "cuda_dense":
+            out = dense_decode_attention(query, key, scaling, num_splits=0)
+        else:
+            out = _dense_sdpa(query, key, scaling)
     elif Q > 1 and getattr(key, "prefill_backend", "reconstruct") == "packed" and query.is_cuda:
         BACKEND_COUNTS["prefill_cuda_packed"] += 1
         out = pa.tiled_compressed_attention(
