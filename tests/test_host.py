@@ -66,6 +66,31 @@ def test_release_bumps_generation_and_waits_for_the_fence():
     assert any(r.generation == 1 for r in again)
 
 
+def test_batch_reservation_and_device_table():
+    """`ensure_many` grows a whole batch or nothing; `DeviceTable` rewrites only
+    the rows whose reservation changed and refuses a step its pages cannot hold."""
+    from winnow_b200.page_pool import DeviceTable
+    p = pool(num_pages=8)
+    p.ensure_many(["a", "b"], [5, 4])                       # 2 + 1 pages
+    assert p.stats()["owned"] == 3
+    with pytest.raises(PoolExhausted):
+        p.ensure_many(["a", "b", "c"], [9, 9, 13])           # 1 + 2 + 4 more > 5 free
+    assert p.stats()["owned"] == 3                           # nothing was taken
+    t = DeviceTable(p, ["a", "b"], width=4, device="cpu")
+    assert t.refresh([5, 4]) == 2
+    assert t.table.tolist() == [[0, 1, -1, -1], [2, -1, -1, -1]]
+    assert t.refresh([6, 4]) == 0                            # nobody crossed a page boundary
+    p.ensure_many(["a", "b"], [6, 5])
+    assert t.refresh([6, 5]) == 1 and t.table[1].tolist() == [2, 3, -1, -1]
+    with pytest.raises(StalePage):
+        t.refresh([6, 9])                                    # b holds 2 pages, 9 tokens need 3
+    p.release("a", Pending())
+    with pytest.raises(StalePage):
+        t.refresh([6, 5])                                    # a's pages are gone
+    with pytest.raises(PoolExhausted):
+        p.ensure_many(["z"], [4 * 9])                        # beyond the per-request limit
+
+
 def test_contract_rejections_on_metadata():
     c = cases.ATTENTION_CASES[3]
     q, okv, _ = oracle_case(c)

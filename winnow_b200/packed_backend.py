@@ -123,6 +123,20 @@ class PagedPackedCache:
             raise RuntimeError("mixed lengths: pass explicit position_ids")
         return self.lengths[0]
 
+    def check(self) -> None:
+        """Raise `StalePage` if a kernel of this forward refused a page id or a
+        position (it skipped the access and set a bit in `self.status`, which
+        both the append and the attention launches report into).  Synchronises:
+        call it where the caller syncs anyway, e.g. before sampling."""
+        if self.status is None:
+            return
+        word = int(self.status.item())
+        if word:
+            self.status.zero_()
+            raise StalePage(f"forward refused part of the batch (status {word:#x}: bit "
+                            f"{_lib.STATUS_BAD_PAGE} page id outside the pool, bit "
+                            f"{_lib.STATUS_BAD_POSITION} position outside the page table)")
+
     def _prepare(self, n: int, device):
         """Once per forward: check ownership and reservation, build the page
         table and the post-append lengths, and copy both to the device.  Never
@@ -173,6 +187,7 @@ class PagedPackedCache:
             handle.table_validated = True      # ids come from validated page refs
         handle.decode_backend = self.decode_backend
         handle.prefill_backend = self.prefill_backend
+        handle.status = self.status             # the attention call reports into the same word
         if last:
             self.lengths = [L + n for L in self.lengths]
         return handle, handle
@@ -358,7 +373,7 @@ def winnow_packed_attention(module, query, key, value, attention_mask, dropout: 
             BACKEND_COUNTS["triton_packed"] += 1
         if backend == "cuda_packed":
             out = packed_decode_attention(
-                query, key, scaling,
+                query, key, scaling, status=getattr(key, "status", None),
                 check_page_ids=not getattr(key, "table_validated", False))
         else:
             out = _reconstruct_sdpa(query, key, scaling)
