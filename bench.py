@@ -229,10 +229,17 @@ def run_ours(args):
         r = measure_workload(name, args, rank, world, local, dev, main=False)
         if rank == 0:
             others[name] = r
+    dequant = None
+    if world == 1 and args.dequant:
+        torch.cuda.empty_cache()
+        dequant = measure_dequant(dev)
     if rank != 0:
         return
     if others:
         line["workloads"] = others
+    if dequant is not None:
+        line["dequant_gbs"] = dequant["gbs"]["tc"]
+        line["dequant"] = dequant
     print(json.dumps(line))
 
 
@@ -411,6 +418,11 @@ def measure_workload(name, args, rank, world, local, dev, main):
     # ---- fused append of one token per sequence (reported beside the step)
     append_us = time_append(w, pool, handles, rank, world, dev, args)
 
+    # ---- prefill chunk of 64 query tokens per sequence over this rank's pages
+    prefill_us = time_prefill(w, handles[0], hq, scale, dev) if main else None
+    if prefill_us is not None:
+        prefill_us = max_over_ranks(prefill_us, world, dev)
+
     # ---- plain streaming read of this rank's pool: the read-only ceiling
     read_gbs = None
     if main:                                                 # slowest rank's figure
@@ -462,6 +474,11 @@ def measure_workload(name, args, rank, world, local, dev, main):
         "hbm_frac_of_8tbs_nominal": alg_total / (ms * 1e-3) / 1e9 / (NOMINAL_HBM_GBS * world),
         "tokens_per_s": w.batch / (ms * 1e-3),
         "append_us": append_us,
+        "prefill_us": prefill_us,
+        "prefill": {"query_tokens": PREFILL_Q, "what": "packed_prefill_attention (wtq_prefill): the last "
+                    f"{PREFILL_Q} tokens of every sequence attend causally over its packed history; "
+                    "device time of the whole call (query permute, rotation, page scan, merge), "
+                    "median of 5 after 2 warm-up calls"},
         "e2e": {"value": e2e_ms * 1e3, "unit": "us",
                 "h2d_bytes_per_step": q_host.numel() * q_host.element_size(),
                 "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
@@ -511,6 +528,72 @@ def time_stream_read(lib, tensor) -> float:
     e.record()
     torch.cuda.synchronize()
     return nbytes * 10 / (s.elapsed_time(e) * 1e-3) / 1e9
+
+
+def measure_dequant(dev) -> dict:
+    """Fused dequantisation (wtq_dequant_mode) of 2^20 packed 4-bit rows, the K
+    side of 8 sequences x 4 kv heads x 32k tokens, to bf16: 64 B of codes and a
+    2 B norm in, 256 B out per row, 338 MB per call (larger than L2, so every
+    call streams from and to HBM).  Device time per call from CUDA events."""
+    from winnow_b200.cache import _get_quantizer, dequantize_rows
+    rows = 1 << 20
+    tq = _get_quantizer(4, 128, dev, 42)
+    g = torch.Generator(device=dev).manual_seed(5)
+    packed = torch.randint(0, 256, (rows, 64), dtype=torch.uint8, device=dev, generator=g)
+    norms = (torch.rand(rows, device=dev, generator=g) * 4 + 0.5).half()
+    outs = {}
+    nbytes = rows * (64 + 2 + 256)
+    peak, kind = measured_peak()
+    result = {"rows": rows, "bits": 4, "out_dtype": "bf16", "bytes_per_call": nbytes, "us": {}, "gbs": {},
+              "modes": {"tc": "tensor cores, fp16 high/low split operands (what bf16/fp16 outputs get "
+                              "by default)",
+                        "tc_fast": "tensor cores, single fp16 operands (the reference's allow_tf32 class)",
+                        "exact": "fp32 on the CUDA cores"}}
+    for mode, reps in (("tc", 20), ("tc_fast", 20), ("exact", 3)):
+        out = torch.empty(rows, 128, dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            dequantize_rows(packed, norms, tq.centroids, tq.Pi, 4, 128, out=out, mode=mode)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            dequantize_rows(packed, norms, tq.centroids, tq.Pi, 4, 128, out=out, mode=mode)
+        e.record()
+        torch.cuda.synchronize()
+        us = s.elapsed_time(e) * 1e3 / reps
+        result["us"][mode] = us
+        result["gbs"][mode] = nbytes / (us * 1e-6) / 1e9
+        outs[mode] = out
+    exact = outs["exact"].float()
+    top = float(exact.abs().max())
+    result["max_abs_diff_vs_exact_over_max"] = {m: float((outs[m].float() - exact).abs().max()) / top
+                                                for m in ("tc", "tc_fast")}
+    result["frac_of_hbm_peak"] = result["gbs"]["tc"] / peak
+    result["peak_kind"] = kind
+    return result
+
+
+PREFILL_Q = 64
+
+
+def time_prefill(w, handle, hq, scale, dev):
+    """Median device time (us) of one chunked-prefill call at PREFILL_Q query
+    tokens per sequence over `handle`'s pages, or None if the chunk kernel does
+    not serve this layout."""
+    from winnow_b200.packed_attention_cuda import packed_prefill_attention, prefill_supported
+    g = torch.Generator().manual_seed(w.seed + 64)
+    q = torch.randn(w.batch, hq, PREFILL_Q, w.head_dim, generator=g).to(dev, w.dtype)
+    if not prefill_supported(q, handle):
+        return None
+    times = []
+    for i in range(2 + 5):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        packed_prefill_attention(q, handle, scale, check_page_ids=False)
+        e.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(s.elapsed_time(e) * 1e3)
+    return statistics.median(times)
 
 
 def _first_seq(handle):
@@ -606,6 +689,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config2", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--dequant", type=int, default=1,
+                    help="1: also time the fused dequantisation kernels (single GPU only)")
     ap.add_argument("--extra", default="headline32k,config3,config4,config5",
                     help="comma list of further workloads reported under \"workloads\" (or none)")
     ap.add_argument("--layers", type=int, default=0, help="layers of pages to rotate over (0=auto)")

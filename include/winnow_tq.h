@@ -221,14 +221,64 @@ int wtq_dense_decode(const void *q, int q_dtype, const int64_t q_strides[2], voi
                      int num_splits, void *workspace, size_t workspace_bytes, int32_t *status,
                      void *stream);
 
+/* Chunked prefill over packed pages: causal attention of the last Q tokens of
+ * every sequence (their K/V already appended, so seq_lens includes them) over
+ * the sequence's packed history, the pages read and decoded once for all query
+ * rows.  Replaces the reference's prefill fallback, dequantize_history +
+ * _reconstruct_sdpa (turboquant_kv/packed_backend.py:192-226), and computes
+ * what tiled_compressed_attention (turboquant_kv/packed_attention.py:260-311)
+ * computes for Q > 1.
+ *
+ *   q    row (b * Q + i) holds query token i of sequence b: element (row, head, d)
+ *        at q + row * q_strides[0] + head * q_strides[1] + d (elements);
+ *   out  the same indexing with out_strides, i.e. a (B, Q, Hq, D) tensor.
+ * Token i sees keys [0, seq_lens[b] - Q + i]; a token that sees none gets zeros.
+ * Requires what the tensor-core decode path requires (head_dim 128, widths
+ * 4/4, 4/6, 6/6, 8/8, power-of-two page size >= 16, Hq / Hkv <= 8, 16-byte
+ * aligned pages); otherwise WTQ_ERR_UNSUPPORTED, and the caller may run the
+ * B * Q rows through wtq_decode instead.  num_splits <= 0 picks the number of
+ * history chunks (wtq_prefill_auto_splits); the workspace must hold
+ * wtq_prefill_workspace_bytes(..., num_splits) for the value used.  Status bits
+ * as for wtq_decode.  Four launches, no allocation, no synchronisation. */
+int wtq_prefill_auto_splits(int B, int Hq, int Hkv, int Q, int max_pages, int S);
+size_t wtq_prefill_workspace_bytes(int B, int Hq, int Hkv, int Q, int D, int num_splits);
+int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2], void *out,
+                const int64_t out_strides[2], const wtq_side_t *k_side, const wtq_side_t *v_side,
+                const int32_t *page_table, int64_t table_stride, const int32_t *seq_lens,
+                float scale, int B, int Hq, int Hkv, int Q, int D, int S, int P, int max_pages,
+                int num_splits, void *workspace, size_t workspace_bytes, int32_t *status,
+                void *stream);
+
 /* Replaces tq_dequant / tq_dequant_cuda (turboquant_kv/kernel.py:78-115,
  * turboquant_kv/csrc/tq_dequant.cu:186-211): N packed rows -> (N, D) of
  * `out_dtype`.  Logical row r is read from source row (r / L) * MAXLEN + r % L
  * (a (planes, MAXLEN, NB) buffer viewed through its first L positions);
- * out[r] = (centroids[codes] @ Pi) * norm. */
+ * out[r] = (centroids[codes] @ Pi) * norm.
+ *
+ * wtq_dequant_mode chooses the arithmetic:
+ *   WTQ_DEQUANT_EXACT    fp32 contraction on the CUDA cores (any D <= 256, any width);
+ *   WTQ_DEQUANT_TC       tensor cores, centroids and Pi each split into fp16 high
+ *                        and low parts, three products accumulated in fp32;
+ *   WTQ_DEQUANT_TC_FAST  tensor cores, single fp16 operands: the accuracy class of
+ *                        the reference's allow_tf32=True (turboquant_kv/kernel.py:69);
+ *   WTQ_DEQUANT_AUTO     TC for fp16/bf16 outputs where the tensor-core kernel
+ *                        applies, EXACT otherwise (what wtq_dequant does).
+ * The tensor-core kernel needs D = 128, a width of 4, 6 or 8, `packed` 16-byte
+ * aligned (8 for 6-bit), `out` 16-byte aligned and MAXLEN < 2^31; an explicit
+ * TC mode outside that returns WTQ_ERR_UNSUPPORTED.  The first tensor-core call
+ * of each (width, mode, dtype) on a device synchronises the stream once to set
+ * the kernel up, so it cannot be made while the stream is capturing (AUTO then
+ * runs EXACT for that call). */
+#define WTQ_DEQUANT_AUTO (-1)
+#define WTQ_DEQUANT_EXACT 0
+#define WTQ_DEQUANT_TC 1
+#define WTQ_DEQUANT_TC_FAST 2
 int wtq_dequant(const uint8_t *packed, const void *norms_f16, const float *centroids,
                 const float *Pi, void *out, int out_dtype, int bw, int D, int64_t N, int64_t L,
                 int64_t MAXLEN, void *stream);
+int wtq_dequant_mode(const uint8_t *packed, const void *norms_f16, const float *centroids,
+                     const float *Pi, void *out, int out_dtype, int bw, int D, int64_t N, int64_t L,
+                     int64_t MAXLEN, int mode, void *stream);
 
 /* Instrumentation; no counterpart in the reference.
  * wtq_launch_count: kernels this library has launched in this process.

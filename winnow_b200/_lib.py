@@ -14,6 +14,7 @@ WTQ_F32, WTQ_F16, WTQ_BF16 = 0, 1, 2
 ORDER_AUTO, ORDER_SEQUENTIAL, ORDER_INTERLEAVED16 = -1, 0, 1
 STATUS_BAD_PAGE, STATUS_BAD_POSITION = 1, 2
 STATUS_LAYOUT, STATUS_SCAN_TIMEOUT = 8, 16
+DEQUANT_AUTO, DEQUANT_EXACT, DEQUANT_TC, DEQUANT_TC_FAST = -1, 0, 1, 2
 
 _DTYPES = {torch.float32: WTQ_F32, torch.float16: WTQ_F16, torch.bfloat16: WTQ_BF16}
 
@@ -84,8 +85,16 @@ _SIGNATURES = {
                                  ctypes.POINTER(c_int64), ctypes.POINTER(c_int64), c_void_p, c_int64,
                                  c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "wtq_prefill_auto_splits": (c_int, [c_int] * 6),
+    "wtq_prefill_workspace_bytes": (c_size_t, [c_int] * 6),
+    "wtq_prefill": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p, ctypes.POINTER(c_int64),
+                            ctypes.POINTER(Side), ctypes.POINTER(Side), c_void_p, c_int64, c_void_p,
+                            c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_size_t, c_void_p, c_void_p]),
     "wtq_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int64, c_int64, c_int64, c_void_p]),
+    "wtq_dequant_mode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                 c_int, c_int64, c_int64, c_int64, c_int, c_void_p]),
 }
 
 _lib = None

@@ -97,15 +97,30 @@ class TurboQuantMSE:
 @torch.no_grad()
 def dequantize_rows(packed: torch.Tensor, norms: torch.Tensor, centroids: torch.Tensor,
                     Pi: torch.Tensor, bit_width: int, head_dim: int,
-                    out: torch.Tensor | None = None, allow_tf32: bool = False) -> torch.Tensor:
+                    out: torch.Tensor | None = None, allow_tf32: bool = False,
+                    mode: str | None = None) -> torch.Tensor:
     """Fused dequantisation of packed rows, the counterpart of the reference's
     `tq_dequant` (turboquant_kv/kernel.py:78-115).
 
     `packed` is (..., NB) uint8 and `norms` (...,) fp16.  A (B, H, L, NB) slice
     of a (B, H, MAXLEN, NB) buffer is read in place through its strides.
     Returns (..., head_dim) in `out`'s dtype (bf16 when `out` is None).
+
+    Arithmetic (`mode`): "exact" is an fp32 contraction on the CUDA cores; "tc"
+    runs on the tensor cores with centroids and Pi split into fp16 high and low
+    parts (three products, fp32 accumulation); "tc_fast" uses single fp16
+    operands, the accuracy class of the reference's `allow_tf32=True`.  With
+    `mode=None`: `allow_tf32=True` asks for "tc_fast" where the tensor-core
+    kernel applies (head_dim 128, widths 4/6/8), otherwise the library picks
+    "tc" for 16-bit outputs it applies to and "exact" for everything else.
     """
-    del allow_tf32                      # the CUDA backend always computes in fp32
+    if mode is None:
+        code = _lib.DEQUANT_AUTO
+        if allow_tf32 and head_dim == 128 and bit_width in (4, 6, 8):
+            code = _lib.DEQUANT_TC_FAST
+    else:
+        code = {"exact": _lib.DEQUANT_EXACT, "tc": _lib.DEQUANT_TC,
+                "tc_fast": _lib.DEQUANT_TC_FAST}[mode]
     dev = _lib.require_cuda(packed, norms, centroids, Pi)
     nb = packed_bytes(head_dim, bit_width)
     if packed.dtype != torch.uint8 or packed.shape[-1] != nb:
@@ -131,10 +146,10 @@ def dequantize_rows(packed: torch.Tensor, norms: torch.Tensor, centroids: torch.
         raise ValueError("out must be contiguous with shape (..., head_dim)")
     if N:
         with torch.cuda.device(dev):
-            _lib.check(_lib.lib().wtq_dequant(
+            _lib.check(_lib.lib().wtq_dequant_mode(
                 src.data_ptr(), nsrc.data_ptr(), centroids.data_ptr(), Pi.data_ptr(),
                 out.data_ptr(), _lib.dtype_code(out.dtype), bit_width, head_dim, N, L, maxlen,
-                _lib.stream_ptr(dev)))
+                code, _lib.stream_ptr(dev)))
     return out
 
 

@@ -13,17 +13,6 @@ size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 // lookup tables of the tensor-core scan: at most 256 entries x 2 sides x 32 lanes
 constexpr size_t kLutBytesMax = 256 * 256;
 
-int device_sms() {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      sms = 148;
-  }
-  return sms;
-}
-
 int clamp_splits(int splits, int max_pages, int S) {
   const int64_t tokens = (int64_t)max_pages * S;
   int64_t tiles = (tokens + 127) / 128;
@@ -313,10 +302,7 @@ __global__ void __launch_bounds__(256) stream_read_kernel(const uint4 *src, size
 extern "C" int wtq_probe_read(const void *src, size_t bytes, uint32_t *sink, void *stream) {
   if (!src || ((uintptr_t)src & 15) || bytes < 16)
     return fail(WTQ_ERR_ARG, "wtq_probe_read: need a 16-byte aligned buffer of at least 16 bytes");
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-    sms = 148;
+  const int sms = device_sms();
   stream_read_kernel<<<sms * 8, 256, 0, (cudaStream_t)stream>>>((const uint4 *)src, bytes / 16, sink);
   note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_probe_read launch");

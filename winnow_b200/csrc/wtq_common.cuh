@@ -18,6 +18,7 @@ char *error_buffer();
 int fail(int code, const char *fmt, ...);
 int check_cuda(cudaError_t e, const char *what);
 void note_launches(int n);
+int device_sms();          // multiprocessors of the current device
 // Recorder of event pairs around the decode page-scan kernel (see
 // wtq_profile_enable); both are no-ops while profiling is off.
 void profile_mark_begin(cudaStream_t stream);

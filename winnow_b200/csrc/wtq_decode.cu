@@ -16,6 +16,7 @@
 #include <algorithm>
 
 #include "wtq_decode.cuh"
+#include "wtq_lut.cuh"
 
 namespace wtq {
 
@@ -53,13 +54,7 @@ __device__ void scan_setup(const ScanSetup &s, const int32_t *seq_lens, int B, i
     write_chunk_prefix(seq_lens, B, chunk_tokens, max_tokens, s.chunk_prefix);
   if (s.lut == nullptr) return;
   for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < s.lut_words; e += gridDim.x * blockDim.x) {
-    const int index = e >> 6, side = (e >> 5) & 1;
-    const int bw = side ? s.bw_v : s.bw_k;
-    const float *cent = side ? s.cent_v : s.cent_k;
-    __half2 h = __floats2half2_rn(0.f, 0.f);
-    if (bw == 4) h = __floats2half2_rn(__ldg(cent + (index & 15)), __ldg(cent + (index >> 4)));
-    else if (index < (1 << bw)) h = __floats2half2_rn(__ldg(cent + index), __ldg(cent + index));
-    s.lut[e] = *reinterpret_cast<uint32_t *>(&h);
+    s.lut[e] = mma::lut_word(e, s.bw_k, s.bw_v, s.cent_k, s.cent_v);
   }
 }
 

@@ -86,6 +86,8 @@ int mma_warps_per_sm(int bw_k, int bw_v);
 bool mma_eligible(const DecodeParams &p);
 int mma_chunk_tokens(int max_tokens, int splits);
 int launch_decode_mma(const DecodeParams &p, const MergeParams &m, cudaStream_t stream);
+int launch_mma_merge(const MergeParams &m, const int32_t *seq_lens, int B, int Hkv, int n_rep,
+                     int chunk_tokens, int max_tokens, cudaStream_t stream);
 int launch_exchange_wait(const uint32_t *flags, int world, uint32_t *state, long long spin_limit,
                          int32_t *status, cudaStream_t stream);
 

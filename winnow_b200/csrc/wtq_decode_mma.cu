@@ -42,6 +42,9 @@
 #include <type_traits>
 
 #include "wtq_decode.cuh"
+#include "wtq_lut.cuh"
+
+#include <atomic>
 
 namespace wtq {
 
@@ -50,7 +53,6 @@ namespace mma {
 constexpr int kTileTokens = 16;
 constexpr int kTilesPerIter = 2;                       // 32 tokens per iteration
 constexpr int kIterTokens = kTileTokens * kTilesPerIter;
-constexpr uint32_t kLutAddr = 0x10000;                 // shared address of the tables
 constexpr uint32_t kPrefixAddr = 2048;                 // chunk prefix copy (>= dynamic smem base)
 constexpr int kPrefixMax = 1024;                       // entries (sequences + 1) it can hold
 constexpr uint32_t kLutBar = kPrefixAddr + 4 * kPrefixMax;    // mbarrier of the tables' copy
@@ -64,7 +66,6 @@ constexpr int kWaitTries = 1 << 18;     // bound of the mbarrier wait (each try 
 // every benchmark shape: the lookups of a warp overlap better than more warps do.
 constexpr int kMaxWarps = 12;
 
-constexpr int lut_entries(int bw) { return bw == 4 ? 256 : (1 << bw); }
 constexpr int cmax(int a, int b) { return a > b ? a : b; }
 constexpr int cmin(int a, int b) { return a < b ? a : b; }
 
@@ -138,140 +139,9 @@ __device__ __forceinline__ void griddep_launch() {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 }
 
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float lds_half(uint32_t a) {
-  unsigned short h;
-  asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(h) : "r"(a));
-  return __half2float(__ushort_as_half(h));
-}
-__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
-  asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(a), "r"(v) : "memory");
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
-  uint32_t d;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
-  return d;
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                         uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
-      "{%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-  __half2 h = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t *>(&h);
-}
-
-// ---- table lookups ----------------------------------------------------------
-// `sel` carries 0x10000, the side bit (values: 0x80) and the lane's bank.
-// 4-bit: entry of byte K (0..3) of `word`, a half2 of the byte's two codes.
-template <int K> __device__ __forceinline__ uint32_t lut_addr(uint32_t word, uint32_t sel) {
-  return __byte_perm(word, sel, 0x7604 | (K << 4));
-}
-template <int K> __device__ __forceinline__ uint32_t lut_byte(uint32_t word, uint32_t sel) {
-  return lds32(lut_addr<K>(word, sel));
-}
-// 6/8-bit: entry {c, c} of code I of the bit stream held in w[0..NW).
-template <int BW, int I, int NW>
-__device__ __forceinline__ uint32_t lut_code(const uint32_t (&w)[NW], uint32_t sel) {
-  constexpr int bit = I * BW, word = bit / 32, off = bit % 32;
-  static_assert(word < NW, "code outside the words held");
-  if constexpr (BW == 8) {
-    return lds32(__byte_perm(w[word], sel, 0x7604 | ((off / 8) << 4)));
-  } else {
-    constexpr uint32_t mask = ((1u << BW) - 1u) << 8;
-    uint32_t x;
-    if constexpr (off + BW <= 32) {
-      x = off >= 8 ? (w[word] >> (off >= 8 ? off - 8 : 0)) : (w[word] << (off < 8 ? 8 - off : 0));
-    } else {                                     // the code straddles two words
-      x = __funnelshift_r(w[word], w[word + 1 < NW ? word + 1 : word], off - 8);
-    }
-    return lds32((x & mask) | sel);
-  }
-}
-// low half of x joined with the high half of y
-__device__ __forceinline__ uint32_t join(uint32_t x, uint32_t y) {
-  return __byte_perm(x, y, 0x7610);
-}
-
-// Words of a lane's share of a packed row: NBYTES at shared address a.
-template <int NBYTES>
-__device__ __forceinline__ void load_words(uint32_t a, uint32_t (&w)[NBYTES / 4]) {
-  if constexpr (NBYTES % 16 == 0) {
-#pragma unroll
-    for (int i = 0; i < NBYTES / 16; ++i) {
-      const uint4 v = lds128(a + 16 * i);
-      w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-    }
-  } else if constexpr (NBYTES % 8 == 0) {
-#pragma unroll
-    for (int i = 0; i < NBYTES / 8; ++i) {
-      const uint2 v = lds64(a + 8 * i);
-      w[2 * i] = v.x; w[2 * i + 1] = v.y;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < NBYTES / 4; ++i) w[i] = lds32(a + 4 * i);
-  }
-}
-
 }  // namespace mma
 
 using namespace mma;
-
-// A-fragment registers of the score MMA for contraction step KS (0..7): the
-// lane holds 32 codes (coordinates 32t..32t+31) of token rows g (w0) and g+8
-// (w1); step KS consumes codes 4KS..4KS+3 of each.
-template <int BW, int KS, int NW>
-__device__ __forceinline__ void key_fragment(const uint32_t (&w0)[NW], const uint32_t (&w1)[NW],
-                                             uint32_t sel, uint32_t (&a)[4]) {
-  if constexpr (BW == 4) {
-    constexpr int j = KS / 2, e = 2 * (KS % 2);
-    a[0] = lut_byte<e>(w0[j], sel);
-    a[1] = lut_byte<e>(w1[j], sel);
-    a[2] = lut_byte<e + 1>(w0[j], sel);
-    a[3] = lut_byte<e + 1>(w1[j], sel);
-  } else {
-    constexpr int i = 4 * KS;
-    a[0] = join(lut_code<BW, i>(w0, sel), lut_code<BW, i + 1>(w0, sel));
-    a[1] = join(lut_code<BW, i>(w1, sel), lut_code<BW, i + 1>(w1, sel));
-    a[2] = join(lut_code<BW, i + 2>(w0, sel), lut_code<BW, i + 3>(w0, sel));
-    a[3] = join(lut_code<BW, i + 2>(w1, sel), lut_code<BW, i + 3>(w1, sel));
-  }
-}
 
 // Value side of one tile: the lane holds coordinates 16g..16g+15 of tokens
 // 2t, 2t+1 (A, B) and 2t+8, 2t+9 (C, D); `at` = address of its 16 codes of
@@ -1266,15 +1136,68 @@ int mma_chunk_tokens(int max_tokens, int splits) {
   return per < kGrain ? kGrain : per;
 }
 
+// Merge of the chunk states written by a tensor-core scan (decode or prefill):
+// `B` rows of `seq_lens`, each with ceil(len / chunk_tokens) chunk states per
+// head, m.num_splits slots apart.  Launched so that it may begin while the scan
+// drains (it waits before it reads).
+int launch_mma_merge(const MergeParams &m, const int32_t *seq_lens, int B, int Hkv, int n_rep,
+                     int chunk_tokens, int max_tokens, cudaStream_t stream) {
+  const int sms = device_sms();
+  static std::atomic<bool> opted_in_dev[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64 || !opted_in_dev[dev & 63].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(merge_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         128 * 128 * (int)sizeof(float));
+    if (e != cudaSuccess) return check_cuda(e, "wtq_decode: merge shared memory opt-in");
+    opted_in_dev[dev & 63].store(true, std::memory_order_release);
+  }
+  cudaLaunchAttribute pdl;
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.stream = stream;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  const int num_groups = B * Hkv;
+  if (num_groups >= 4 * sms && m.num_splits <= kSmallMergeChunks) {
+    // many groups: small blocks, several resident per SM, all heads of a group
+    // in one block.  (With fewer groups the persistent kernel below is faster,
+    // also against this kernel run with fewer heads per block: measured.)
+    const int heads = n_rep;
+    cfg.gridDim = dim3((unsigned)num_groups, (unsigned)(n_rep / heads));
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    e = cudaLaunchKernelEx(&cfg, merge_small_kernel, m, seq_lens, Hkv, n_rep, heads, chunk_tokens,
+                           max_tokens);
+    note_launches(1);
+    return check_cuda(e, "wtq_decode merge launch");
+  }
+  // heads per merge block: all of the group when there are many groups, fewer
+  // (down to one) when a handful of long sequences would leave most SMs idle
+  int hpb = n_rep;
+  while (hpb > 1 && hpb % 2 == 0 && (int64_t)num_groups * (n_rep / hpb) < sms / 2) hpb /= 2;
+  // one merge block is resident per SM: no more blocks than SMs, each walks its groups
+  const int passes = n_rep / hpb;
+  cfg.gridDim = dim3((unsigned)std::min(num_groups, std::max(1, sms / passes)), (unsigned)passes);
+  cfg.blockDim = dim3(kMergeThreads);
+  cfg.dynamicSmemBytes = 128 * 128 * sizeof(float);
+  e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, seq_lens, num_groups, Hkv, n_rep, hpb,
+                         chunk_tokens, max_tokens);
+  note_launches(1);
+  return check_cuda(e, "wtq_decode merge launch");
+}
+
 template <int BWK, int BWV>
 static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cudaStream_t stream) {
   using C = Cfg<BWK, BWV>;
   // function attributes belong to the device the call runs on
-  static bool opted_in_dev[64] = {};
+  static std::atomic<bool> opted_in_dev[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  bool &opted_in = opted_in_dev[dev & 63];
-  if (!opted_in) {
+  std::atomic<bool> &opted_in = opted_in_dev[dev & 63];
+  if (dev >= 64 || !opted_in.load(std::memory_order_acquire)) {   // setting twice is harmless
     cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<BWK, BWV, true>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)C::kDynamicSmem);
@@ -1282,10 +1205,7 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
     e = cudaFuncSetAttribute(decode_mma_kernel<BWK, BWV, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kDynamicSmem);
     if (e != cudaSuccess) return check_cuda(e, "wtq_decode: shared memory opt-in");
-    e = cudaFuncSetAttribute(merge_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             128 * 128 * (int)sizeof(float));
-    if (e != cudaSuccess) return check_cuda(e, "wtq_decode: merge shared memory opt-in");
-    opted_in = true;
+    opted_in.store(true, std::memory_order_release);
   }
   const int max_tokens = p.max_pages * p.S;
   const int chunk_tokens = mma_chunk_tokens(max_tokens, p.num_splits);
@@ -1309,44 +1229,12 @@ static int launch_one(const DecodeParams &p, const MergeParams &m, int sms, cuda
                             : cudaLaunchKernelEx(&cfg, decode_mma_kernel<BWK, BWV, false>, p, chunk_tokens);
   profile_mark_end(stream);
   if (e != cudaSuccess) return check_cuda(e, "wtq_decode mma launch");
-  const int num_groups_all = p.B * p.Hkv;
-  if (num_groups_all >= 4 * sms && p.num_splits <= kSmallMergeChunks) {
-    // many groups: small blocks, several resident per SM, all heads of a group
-    // in one block.  (With fewer groups the persistent kernel below is faster,
-    // also against this kernel run with fewer heads per block: measured.)
-    const int heads = p.n_rep;
-    cfg.gridDim = dim3((unsigned)num_groups_all, (unsigned)(p.n_rep / heads));
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = 0;
-    e = cudaLaunchKernelEx(&cfg, merge_small_kernel, m, p.seq_lens, p.Hkv, p.n_rep, heads,
-                           chunk_tokens, max_tokens);
-    note_launches(2);
-    return check_cuda(e, "wtq_decode merge launch");
-  }
-  // heads per merge block: all of the group when there are many groups, fewer
-  // (down to one) when a handful of long sequences would leave most SMs idle
-  int hpb = p.n_rep;
-  while (hpb > 1 && hpb % 2 == 0 && (int64_t)p.B * p.Hkv * (p.n_rep / hpb) < sms / 2) hpb /= 2;
-  const int num_groups = p.B * p.Hkv;
-  // one merge block is resident per SM: no more blocks than SMs, each walks its groups
-  const int passes = p.n_rep / hpb;
-  cfg.gridDim = dim3((unsigned)std::min(num_groups, std::max(1, sms / passes)), (unsigned)passes);
-  cfg.blockDim = dim3(kMergeThreads);
-  cfg.dynamicSmemBytes = 128 * 128 * sizeof(float);
-  e = cudaLaunchKernelEx(&cfg, merge_group_kernel, m, p.seq_lens, num_groups, p.Hkv, p.n_rep, hpb,
-                         chunk_tokens, max_tokens);
-  note_launches(2);
-  return check_cuda(e, "wtq_decode merge launch");
+  note_launches(1);
+  return launch_mma_merge(m, p.seq_lens, p.B, p.Hkv, p.n_rep, chunk_tokens, max_tokens, stream);
 }
 
 int launch_decode_mma(const DecodeParams &p, const MergeParams &m, cudaStream_t stream) {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    sms = n > 0 ? n : 148;
-  }
+  const int sms = device_sms();
   if (p.k.bw == 4 && p.v.bw == 4) return launch_one<4, 4>(p, m, sms, stream);
   if (p.k.bw == 4 && p.v.bw == 6) return launch_one<4, 6>(p, m, sms, stream);
   if (p.k.bw == 6 && p.v.bw == 6) return launch_one<6, 6>(p, m, sms, stream);

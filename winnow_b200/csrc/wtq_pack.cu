@@ -28,6 +28,23 @@ int check_cuda(cudaError_t e, const char *what) {
 
 static std::atomic<uint64_t> g_launches{0};
 void note_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// Multiprocessor count of the current device (cached per device; the cache is
+// only ever written with the value the driver reports, so concurrent first
+// calls are harmless).
+int device_sms() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::atomic<int> &slot = cached[dev & 63];
+  int sms = dev < 64 ? slot.load(std::memory_order_relaxed) : 0;
+  if (sms == 0) {
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+    if (dev < 64) slot.store(sms, std::memory_order_relaxed);
+  }
+  return sms;
+}
 uint64_t launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
 static std::mutex g_profile_lock;

@@ -1,0 +1,655 @@
+// Chunked prefill straight from the packed pages: causal attention of a chunk
+// of Q query tokens per sequence over that sequence's packed history, every
+// page read and decoded once for all the query rows that share it.  Replaces
+// the reference's prefill fallback, which dequantizes the whole history of
+// each sequence to the model dtype and calls SDPA
+// (turboquant_kv/packed_backend.py:192-226), and this library's own earlier
+// form of it (B * Q one-token rows through the decode kernels, the history
+// read Q times).
+//
+// Work is cut into items (sequence b, kv head, block of 256 query rows, chunk
+// of the history); the query rows of a kv head are (token i, head r) pairs in
+// token-major order, so the causal length never decreases along them.  A block
+// of eight warps takes items from a counter.  Per item it loads its 256 rotated
+// query rows as fp16 into shared memory once, then walks the chunk in tiles of
+// 64 tokens:
+//
+//   copy     cp.async brings the tile's packed K and V rows and their fp16 norms
+//            into a landing buffer, one tile ahead of the arithmetic;
+//   decode   each warp turns one 16-token group of one side into fp16 centroid
+//            values through the per-lane lookup tables (wtq_lut.cuh) and stores
+//            them as a [token][coordinate] tile, 16-byte pieces XOR-swizzled by
+//            the row so that ldmatrix reads it without bank conflicts;
+//   scores   each warp owns 32 query rows: S = Q K^T with mma.m16n8k16 (A: query
+//            fragments by ldmatrix, B: key tile by ldmatrix), times the key
+//            norms, causal mask where the tile reaches a row's limit;
+//   softmax  online, in the exp2 domain, on the score fragments in registers;
+//   values   O += (P * value norms) V, the probability fragments feeding the MMA
+//            as A operands directly, V by ldmatrix.trans.
+//
+// fp16 scores are exact enough while they are small; a warp whose tile holds a
+// score beyond 8 (log2 domain) recomputes that tile's scores in fp32 from the
+// packed codes.  At the end of the chunk every row that sees the chunk writes
+// its state (reference maximum, sum, un-normalised accumulator in the value
+// basis) in the layout of the decode scan, and the decode path's merge kernels
+// combine the chunks, rotate back and store.
+#include <algorithm>
+#include <atomic>
+
+#include "wtq_decode.cuh"
+#include "wtq_lut.cuh"
+
+namespace wtq {
+namespace pf {
+
+constexpr int kWarps = 8, kThreads = 32 * kWarps;
+constexpr int kRows = 32 * kWarps;              // query rows per item
+constexpr int kTile = 64;                       // tokens per tile
+constexpr uint32_t kBase = 1024;                // dynamic shared memory is assumed to start at or below this
+constexpr uint32_t kKTile = kBase;              // [64][128] fp16
+constexpr uint32_t kVTile = kKTile + kTile * 256;
+constexpr uint32_t kNormK = kVTile + kTile * 256;   // 64 floats each
+constexpr uint32_t kNormV = kNormK + kTile * 4;
+constexpr uint32_t kItem = kNormV + kTile * 4;      // the item being worked on
+static_assert(kItem + 16 <= mma::kLutAddr, "tiles must end below the lookup tables");
+constexpr float kPreciseAbove = 8.f;            // |score| (log2 domain) beyond which fp16 is not trusted
+
+struct Params {
+  DecodeSideDev k, v;
+  const float *q_rot;        // (B * Q, Hq, 128) fp32, times scale * log2(e)
+  const int32_t *page_table;
+  int64_t table_stride;
+  const int32_t *seq_lens;   // (B)
+  int32_t *row_lens;         // (B * Q) causal lengths, written here for the merge
+  int B, Hq, Hkv, n_rep, Q, S, P, max_pages, max_tokens;
+  int num_splits, chunk_tokens, row_blocks;
+  float *part_acc, *part_m, *part_l;
+  int32_t *status, *work_counter;
+  const uint32_t *lut;
+};
+
+template <int BWK, int BWV> struct Map {
+  static constexpr int kNBK = 16 * BWK, kNBV = 16 * BWV;
+  static constexpr uint32_t kLutBytes =
+      (uint32_t)(mma::lut_entries(BWK) > mma::lut_entries(BWV) ? mma::lut_entries(BWK)
+                                                                : mma::lut_entries(BWV)) * 256u;
+  static constexpr uint32_t kQTile = mma::kLutAddr + kLutBytes;        // [256][128] fp16
+  static constexpr uint32_t kRaw = kQTile + kRows * 256;
+  // landing buffer of one tile: K rows, V rows, K norms, V norms
+  static constexpr uint32_t kRawV = kTile * kNBK;
+  static constexpr uint32_t kRawNK = kRawV + kTile * kNBV;
+  static constexpr uint32_t kRawNV = kRawNK + kTile * 2;
+  static constexpr uint32_t kRawBytes = kRawNV + kTile * 2;
+  static constexpr uint32_t kDynamic = kRaw + 2 * kRawBytes;
+  static_assert(kDynamic <= 227u * 1024u, "shared memory budget");
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t a, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t a, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+__device__ __forceinline__ void sts64u(uint32_t a, uint32_t x, uint32_t y) {
+  asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+// 16 bytes global -> shared; `bytes` = 16, or 0 to fill the piece with zeros
+__device__ __forceinline__ void copy16(uint32_t dst, const void *src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes)
+               : "memory");
+}
+
+// Address of 16-byte piece `piece` (0..15) of row `row` in a [rows][128] fp16 tile.
+__device__ __forceinline__ uint32_t tile_at(uint32_t tile, int row, int piece) {
+  return tile + (uint32_t)row * 256u + (uint32_t)((piece ^ (row & 7)) << 4);
+}
+
+// Eight consecutive centroid values (fp16) of a lane's share of a packed row:
+// codes 8 J .. 8 J + 7 of the 32 the words hold.
+template <int BW, int J>
+__device__ __forceinline__ void decode_piece(const uint32_t (&w)[BW], uint32_t sel, uint32_t (&f)[4]) {
+  if constexpr (BW == 4) {
+    f[0] = lut_byte<0>(w[J], sel); f[1] = lut_byte<1>(w[J], sel);
+    f[2] = lut_byte<2>(w[J], sel); f[3] = lut_byte<3>(w[J], sel);
+  } else {
+    f[0] = join(lut_code<BW, 8 * J>(w, sel), lut_code<BW, 8 * J + 1>(w, sel));
+    f[1] = join(lut_code<BW, 8 * J + 2>(w, sel), lut_code<BW, 8 * J + 3>(w, sel));
+    f[2] = join(lut_code<BW, 8 * J + 4>(w, sel), lut_code<BW, 8 * J + 5>(w, sel));
+    f[3] = join(lut_code<BW, 8 * J + 6>(w, sel), lut_code<BW, 8 * J + 7>(w, sel));
+  }
+}
+
+// One warp decodes tokens 16 u .. 16 u + 15 of one side: the lane (g, t) takes
+// rows g and g + 8 and coordinates 32 t .. 32 t + 31 of each.
+template <int BW>
+__device__ __forceinline__ void decode_group(uint32_t raw, uint32_t tile, uint32_t sel, int u, int g, int t) {
+  constexpr int NB = 16 * BW;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = 16 * u + g + 8 * h;
+    uint32_t w[BW];
+    load_words<4 * BW>(raw + (uint32_t)row * NB + (uint32_t)t * (4 * BW), w);
+    uint32_t f[4];
+    decode_piece<BW, 0>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 0), f[0], f[1], f[2], f[3]);
+    decode_piece<BW, 1>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 1), f[0], f[1], f[2], f[3]);
+    decode_piece<BW, 2>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 2), f[0], f[1], f[2], f[3]);
+    decode_piece<BW, 3>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 3), f[0], f[1], f[2], f[3]);
+  }
+}
+
+// fp32 scores of a warp's tile from the packed codes: s[m][n][e] for rows
+// 16 m + g + 8 (e >> 1) and tokens 8 n + 2 t + (e & 1), without the key norms.
+// `q[m][h]` points at the row's rotated query (null: the row does not exist).
+template <int BW>
+__device__ __noinline__ void precise_scores(uint32_t raw_k, const float *const (&q)[2][2], int t,
+                                            const float *centroids, float (&s)[2][8][4]) {
+  constexpr int NB = 16 * BW;
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[m][n][e] = 0.f;
+#pragma unroll 1
+  for (int d = 0; d < 128; ++d) {
+    const int bit = d * BW, b0 = bit >> 3, sh = bit & 7;
+    float qv[2][2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) qv[m][h] = q[m][h] ? __ldg(q[m][h] + d) : 0.f;
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t at = raw_k + (uint32_t)(8 * n + 2 * t + c) * NB + b0;
+        uint32_t x = lds_u8(at);
+        if (sh + BW > 8) x |= lds_u8(at + 1) << 8;
+        const float cv = __ldg(centroids + ((x >> sh) & ((1u << BW) - 1u)));
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          s[m][n][c] = fmaf(qv[m][0], cv, s[m][n][c]);
+          s[m][n][2 + c] = fmaf(qv[m][1], cv, s[m][n][2 + c]);
+        }
+      }
+  }
+}
+
+template <int BWK, int BWV>
+__global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
+  using M = Map<BWK, BWV>;
+  extern __shared__ __align__(128) uint8_t dyn_smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if ((uint32_t)__cvta_generic_to_shared(dyn_smem) > kBase) {   // layout assumption broken
+    if (p.status && tid == 0) atomicOr(p.status, WTQ_STATUS_LAYOUT);
+    return;
+  }
+  constexpr uint32_t kFull = 0xffffffffu;
+  // causal length of every query row, for the merge
+  for (int i = blockIdx.x * kThreads + tid; i < p.B * p.Q; i += gridDim.x * kThreads) {
+    int L = p.seq_lens[i / p.Q];
+    L = L < 0 ? 0 : (L > p.max_tokens ? p.max_tokens : L);
+    const int len = L - p.Q + 1 + i % p.Q;
+    p.row_lens[i] = len < 0 ? 0 : len;
+  }
+  // lookup tables (built by the rotation launch)
+  for (int i = tid; i < (int)(M::kLutBytes / 16); i += kThreads) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p.lut) + i);
+    sts128(mma::kLutAddr + 16u * i, v.x, v.y, v.z, v.w);
+  }
+  const uint32_t sel_k = mma::kLutAddr | (uint32_t)(lane << 2), sel_v = sel_k | 0x80u;
+  const int R = p.Q * p.n_rep;                              // query rows per (sequence, kv head)
+  const int items = p.B * p.Hkv * p.row_blocks * p.num_splits;
+  const int page_shift = 31 - __clz(p.S);
+
+  for (;;) {
+    __syncthreads();                                        // everyone is done with the previous item
+    if (tid == 0) sts32(kItem, (uint32_t)atomicAdd(p.work_counter, 1));
+    __syncthreads();
+    const int item = (int)lds32(kItem);
+    if (item >= items) break;
+    // chunks vary fastest, so blocks working at the same time share the query rows in L2
+    const int chunk = item % p.num_splits;
+    const int rb = (item / p.num_splits) % p.row_blocks;
+    const int kvh = (item / (p.num_splits * p.row_blocks)) % p.Hkv;
+    const int b = item / (p.num_splits * p.row_blocks * p.Hkv);
+    int L = p.seq_lens[b];
+    L = L < 0 ? 0 : (L > p.max_tokens ? p.max_tokens : L);
+    const int row_lo = rb * kRows;
+    const int row_hi = min(R, row_lo + kRows);             // rows [row_lo, row_hi) exist
+    auto length_of = [&](int row) {                         // causal length of a row of this group
+      const int len = L - p.Q + 1 + row / p.n_rep;
+      return len < 0 ? 0 : len;
+    };
+    const int start = chunk * p.chunk_tokens;
+    const int len_last = length_of(row_hi - 1);
+    if (row_lo >= R || start >= len_last) continue;         // no row of the block sees this chunk
+    const int end = min(start + p.chunk_tokens, len_last);
+    const int ntiles = (end - start + kTile - 1) / kTile;
+
+    // ---- this lane's four rows ------------------------------------------------
+    const int wrow0 = row_lo + 32 * warp;
+    int limit[2][2];                                        // first token a row does NOT see, within the chunk
+    const float *qptr[2][2];
+    int64_t prow[2][2];                                     // index of the row's chunk state (-1: none)
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = wrow0 + 16 * m + 8 * h + g;
+        const bool exists = row < row_hi;
+        const int i = row / p.n_rep, r = row - i * p.n_rep;
+        const int len = exists ? length_of(row) : 0;
+        limit[m][h] = min(len, start + p.chunk_tokens);
+        const int64_t qrow = ((int64_t)b * p.Q + i) * p.Hq + kvh * p.n_rep + r;
+        qptr[m][h] = exists ? p.q_rot + qrow * 128 : nullptr;
+        prow[m][h] = exists && len > start ? qrow * p.num_splits + chunk : -1;
+      }
+    // rows are in causal order: the warp's first and last existing rows bound its limits
+    const int warp_hi = wrow0 < row_hi ? min(length_of(min(wrow0 + 31, row_hi - 1)), start + p.chunk_tokens) : 0;
+    const int warp_lo = wrow0 < row_hi ? min(length_of(wrow0), start + p.chunk_tokens) : 0;
+    const bool warp_on = warp_hi > start;
+
+    // ---- query rows -> fp16 tile -------------------------------------------------
+    for (int e = tid; e < kRows * 32; e += kThreads) {      // 32 float4 per row
+      const int lr = e >> 5, c4 = e & 31, row = row_lo + lr;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row < row_hi) {
+        const int i = row / p.n_rep, r = row - i * p.n_rep;
+        const int64_t qrow = ((int64_t)b * p.Q + i) * p.Hq + kvh * p.n_rep + r;
+        v = __ldg(reinterpret_cast<const float4 *>(p.q_rot + qrow * 128) + c4);
+      }
+      sts64u(tile_at(M::kQTile, lr, c4 >> 1) + (uint32_t)(c4 & 1) * 8u, pack_half2(v.x, v.y),
+             pack_half2(v.z, v.w));
+    }
+
+    // ---- copy of one tile into a landing buffer ----------------------------------
+    const int32_t *table = p.page_table + (int64_t)b * p.table_stride;
+    auto issue = [&](int j) {
+      const uint32_t raw = M::kRaw + (uint32_t)(j & 1) * M::kRawBytes;
+      const int tok0 = start + j * kTile;
+      constexpr int kPiecesK = kTile * M::kNBK / 16, kPiecesV = kTile * M::kNBV / 16;
+      constexpr int kPieces = kPiecesK + kPiecesV + 16;     // + 8 + 8 pieces of norms
+      for (int c = tid; c < kPieces; c += kThreads) {
+        int side, tok, off;                                  // side 0/1: codes, 2/3: norms
+        uint32_t dst;
+        if (c < kPiecesK) {
+          side = 0; tok = c / (M::kNBK / 16); off = (c - tok * (M::kNBK / 16)) * 16; dst = raw + 16u * c;
+        } else if (c < kPiecesK + kPiecesV) {
+          const int cc = c - kPiecesK;
+          side = 1; tok = cc / (M::kNBV / 16); off = (cc - tok * (M::kNBV / 16)) * 16;
+          dst = raw + M::kRawV + 16u * cc;
+        } else {
+          const int cc = c - kPiecesK - kPiecesV;            // eight tokens of norms per piece
+          side = 2 + (cc >> 3); tok = (cc & 7) * 8; off = 0;
+          dst = raw + (side == 2 ? M::kRawNK : M::kRawNV) + 16u * (cc & 7);
+        }
+        const int token = tok0 + tok;
+        int bytes = token < end ? 16 : 0;
+        const void *src = p.k.pages;                         // any valid address when nothing is read
+        if (bytes) {
+          const int page = table[token >> page_shift], pos = token & (p.S - 1);
+          if (page < 0 || page >= p.P) {
+            if (p.status) atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+            bytes = 0;
+          } else if (side < 2) {
+            const DecodeSideDev &sd = side ? p.v : p.k;
+            src = sd.pages + (int64_t)page * sd.page_stride + (int64_t)kvh * sd.head_stride +
+                  (int64_t)pos * sd.nb + off;
+          } else {
+            const DecodeSideDev &sd = side == 3 ? p.v : p.k;
+            src = sd.norms + (int64_t)page * sd.norm_page_stride + (int64_t)kvh * sd.norm_head_stride + pos;
+          }
+        }
+        copy16(dst, src, bytes);
+      }
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    issue(0);
+
+    float o[2][16][4];                                      // rows x coordinates of the value basis
+    float mx[2][2], sum[2][2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[m][n][e] = 0.f;
+      mx[m][0] = mx[m][1] = -INFINITY;
+      sum[m][0] = sum[m][1] = 0.f;
+    }
+
+    for (int j = 0; j < ntiles; ++j) {
+      const uint32_t raw = M::kRaw + (uint32_t)(j & 1) * M::kRawBytes;
+      const int tok0 = start + j * kTile;
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      __syncthreads();       // the tile has landed for everyone; everyone is done with the previous tiles
+      // ---- decode: warps 0..3 the four key groups, warps 4..7 the value groups ------
+      if (warp < 4) {
+        decode_group<BWK>(raw, kKTile, sel_k, warp, g, t);
+        if (lane < 16) sts32(kNormK + 4u * (16 * warp + lane),
+                             __float_as_uint(lds_half(raw + M::kRawNK + 2u * (16 * warp + lane))));
+      } else {
+        decode_group<BWV>(raw + M::kRawV, kVTile, sel_v, warp - 4, g, t);
+        if (lane < 16) sts32(kNormV + 4u * (16 * (warp - 4) + lane),
+                             __float_as_uint(lds_half(raw + M::kRawNV + 2u * (16 * (warp - 4) + lane))));
+      }
+      __syncthreads();
+      if (j + 1 < ntiles) issue(j + 1);
+      if (!warp_on || tok0 >= warp_hi) continue;            // no row of this warp sees the tile
+
+      // ---- scores -------------------------------------------------------------------
+      float s[2][8][4];
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[m][n][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t a[2][4];
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+          ldmatrix_x4(tile_at(M::kQTile, 32 * warp + 16 * m + (lane & 7) + 8 * ((lane >> 3) & 1),
+                              2 * ks + (lane >> 4)), a[m]);
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          uint32_t kb[4];
+          ldmatrix_x4(tile_at(kKTile, 16 * np + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), kb);
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            mma16816(s[m][2 * np], a[m][0], a[m][1], a[m][2], a[m][3], kb[0], kb[1]);
+            mma16816(s[m][2 * np + 1], a[m][0], a[m][1], a[m][2], a[m][3], kb[2], kb[3]);
+          }
+        }
+      }
+      float nk[8][2];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const float2 v = lds_f2(kNormK + 4u * (8 * n + 2 * t));
+        nk[n][0] = v.x; nk[n][1] = v.y;
+      }
+      const bool masked = tok0 + kTile > warp_lo;            // some row of the warp stops inside the tile
+      float top = 0.f;
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[m][n][e] *= nk[n][e & 1];
+            const bool seen = !masked || tok0 + 8 * n + 2 * t + (e & 1) < limit[m][e >> 1];
+            top = fmaxf(top, seen ? fabsf(s[m][n][e]) : 0.f);
+          }
+      if (__any_sync(kFull, !(top <= kPreciseAbove))) {      // also taken for NaN
+        precise_scores<BWK>(raw, qptr, t, p.k.centroids, s);
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+          for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[m][n][e] *= nk[n][e & 1];
+      }
+      if (masked) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+          for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (tok0 + 8 * n + 2 * t + (e & 1) >= limit[m][e >> 1]) s[m][n][e] = -INFINITY;
+      }
+
+      // ---- online softmax -------------------------------------------------------------
+      float ref[2][2];                                       // finite stand-in for the row maximum
+      bool grew = false;
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float v = -INFINITY;
+#pragma unroll
+          for (int n = 0; n < 8; ++n) v = max3(v, s[m][n][2 * h], s[m][n][2 * h + 1]);
+          v = fmaxf(v, __shfl_xor_sync(kFull, v, 1));
+          v = fmaxf(v, __shfl_xor_sync(kFull, v, 2));
+          grew |= v > mx[m][h];
+          ref[m][h] = v;
+        }
+      if (__any_sync(kFull, grew)) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          float scale[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const float now = fmaxf(mx[m][h], ref[m][h]);
+            scale[h] = now == -INFINITY ? 1.f : ex2(mx[m][h] - now);   // ex2(-inf) = 0 on the first tile
+            mx[m][h] = now;
+            sum[m][h] *= scale[h];
+          }
+#pragma unroll
+          for (int n = 0; n < 16; ++n) {
+            o[m][n][0] *= scale[0]; o[m][n][1] *= scale[0];
+            o[m][n][2] *= scale[1]; o[m][n][3] *= scale[1];
+          }
+        }
+      }
+      float nv[8][2];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const float2 v = lds_f2(kNormV + 4u * (8 * n + 2 * t));
+        nv[n][0] = v.x; nv[n][1] = v.y;
+      }
+      uint32_t pa[2][8][2];                                  // P * value norm as fp16 pairs
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        const float base0 = mx[m][0] == -INFINITY ? 0.f : mx[m][0];
+        const float base1 = mx[m][1] == -INFINITY ? 0.f : mx[m][1];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const float p0 = ex2(s[m][n][0] - base0), p1 = ex2(s[m][n][1] - base0);
+          const float p2 = ex2(s[m][n][2] - base1), p3 = ex2(s[m][n][3] - base1);
+          sum[m][0] += p0 + p1;
+          sum[m][1] += p2 + p3;
+          // a masked token has probability exactly 0; its norm may be anything
+          pa[m][n][0] = pack_half2(p0 == 0.f ? 0.f : p0 * nv[n][0], p1 == 0.f ? 0.f : p1 * nv[n][1]);
+          pa[m][n][1] = pack_half2(p2 == 0.f ? 0.f : p2 * nv[n][0], p3 == 0.f ? 0.f : p3 * nv[n][1]);
+        }
+      }
+
+      // ---- values ---------------------------------------------------------------------
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+        for (int dp = 0; dp < 8; ++dp) {
+          uint32_t vb[4];
+          ldmatrix_x4_trans(tile_at(kVTile, 16 * kk + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * dp + (lane >> 4)), vb);
+#pragma unroll
+          for (int m = 0; m < 2; ++m) {
+            mma16816(o[m][2 * dp], pa[m][2 * kk][0], pa[m][2 * kk][1], pa[m][2 * kk + 1][0],
+                     pa[m][2 * kk + 1][1], vb[0], vb[1]);
+            mma16816(o[m][2 * dp + 1], pa[m][2 * kk][0], pa[m][2 * kk][1], pa[m][2 * kk + 1][0],
+                     pa[m][2 * kk + 1][1], vb[2], vb[3]);
+          }
+        }
+      }
+    }
+
+    // ---- chunk states ---------------------------------------------------------------------
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float l = sum[m][h];
+        l += __shfl_xor_sync(kFull, l, 1);
+        l += __shfl_xor_sync(kFull, l, 2);
+        if (prow[m][h] < 0) continue;
+        float2 *dst = reinterpret_cast<float2 *>(p.part_acc + prow[m][h] * 128 + 2 * t);
+#pragma unroll
+        for (int n = 0; n < 16; ++n) dst[4 * n] = make_float2(o[m][n][2 * h], o[m][n][2 * h + 1]);
+        if (t == 0) {
+          p.part_m[prow[m][h]] = mx[m][h];
+          p.part_l[prow[m][h]] = l;
+        }
+      }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <int BWK, int BWV>
+int launch(const Params &p, cudaStream_t stream) {
+  using M = Map<BWK, BWV>;
+  static std::atomic<bool> opted_in_dev[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64 || !opted_in_dev[dev & 63].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_kernel<BWK, BWV>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)M::kDynamic);
+    if (e != cudaSuccess) return check_cuda(e, "wtq_prefill: shared memory opt-in");
+    opted_in_dev[dev & 63].store(true, std::memory_order_release);
+  }
+  const int64_t items = (int64_t)p.B * p.Hkv * p.row_blocks * p.num_splits;
+  const int grid = (int)std::min<int64_t>(items, device_sms());
+  prefill_kernel<BWK, BWV><<<grid, kThreads, M::kDynamic, stream>>>(p);
+  note_launches(1);
+  return check_cuda(cudaGetLastError(), "wtq_prefill launch");
+}
+
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Tokens per chunk: a multiple of the tile, at least 256.
+int chunk_tokens_for(int max_tokens, int splits) {
+  int tokens = (max_tokens + splits - 1) / splits;
+  tokens = (tokens + kTile - 1) / kTile * kTile;
+  return tokens < 256 ? 256 : tokens;
+}
+
+}  // namespace pf
+}  // namespace wtq
+
+using namespace wtq;
+
+extern "C" int wtq_prefill_auto_splits(int B, int Hq, int Hkv, int Q, int max_pages, int S) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Q < 1 || max_pages < 1 || S < 1 || Hq % Hkv) return 1;
+  const int64_t max_tokens = (int64_t)max_pages * S;
+  const int row_blocks = (Q * (Hq / Hkv) + pf::kRows - 1) / pf::kRows;
+  const int64_t groups = (int64_t)B * Hkv * row_blocks;
+  // about four items per multiprocessor, chunks of at least 256 tokens
+  int64_t splits = (4 * (int64_t)device_sms() + groups - 1) / groups;
+  const int64_t most = std::max<int64_t>(1, max_tokens / 256);
+  splits = std::max<int64_t>(1, std::min<int64_t>(splits, std::min<int64_t>(most, 256)));
+  // chunk sizes round up to whole tiles: drop chunks that would stay empty
+  const int tokens = pf::chunk_tokens_for((int)max_tokens, (int)splits);
+  return (int)((max_tokens + tokens - 1) / tokens);
+}
+
+extern "C" size_t wtq_prefill_workspace_bytes(int B, int Hq, int Hkv, int Q, int D, int num_splits) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Q < 1 || D < 1 || num_splits < 1) return 0;
+  const size_t rows = (size_t)B * Q * Hq;
+  return 256 + pf::round_up((size_t)B * Q * sizeof(int32_t), 256) +
+         pf::round_up(rows * D * sizeof(float), 256) +
+         pf::round_up(rows * num_splits * D * sizeof(float), 256) +
+         2 * pf::round_up(rows * num_splits * sizeof(float), 256) + 256 * 256;
+}
+
+extern "C" int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2], void *out,
+                           const int64_t out_strides[2], const wtq_side_t *k_side,
+                           const wtq_side_t *v_side, const int32_t *page_table,
+                           int64_t table_stride, const int32_t *seq_lens, float scale, int B, int Hq,
+                           int Hkv, int Q, int D, int S, int P, int max_pages, int num_splits,
+                           void *workspace, size_t workspace_bytes, int32_t *status, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (Q < 1) return fail(WTQ_ERR_ARG, "wtq_prefill: need Q >= 1");
+  if (B > 0 && (int64_t)B * Q > (int64_t)1 << 24)
+    return fail(WTQ_ERR_ARG, "wtq_prefill: B * Q is limited to 2^24 query tokens");
+  // the rows of the call are the B * Q query tokens; everything the decode entry
+  // checks about buffers, strides and shapes holds for them as for B sequences
+  if (int rc = decode_validate(q, dtype, q_strides, out, out_strides, false, k_side, v_side,
+                               page_table, seq_lens, B * Q, Hq, Hkv, D, S, P, max_pages))
+    return rc;
+  if (B == 0) return WTQ_OK;
+  if (!workspace) return fail(WTQ_ERR_ARG, "wtq_prefill: null workspace");
+  const int max_tokens = max_pages * S;
+  int splits = num_splits > 0 ? num_splits : wtq_prefill_auto_splits(B, Hq, Hkv, Q, max_pages, S);
+  splits = std::min(splits, std::max(1, max_tokens / pf::kTile));
+  splits = std::min(splits, 256);
+  const int chunk_tokens = pf::chunk_tokens_for(max_tokens, splits);
+  splits = (max_tokens + chunk_tokens - 1) / chunk_tokens;
+  const size_t need = wtq_prefill_workspace_bytes(B, Hq, Hkv, Q, D, splits);
+  if (workspace_bytes < need)
+    return fail(WTQ_ERR_WORKSPACE, "wtq_prefill: workspace %zu < %zu bytes", workspace_bytes, need);
+
+  pf::Params p;
+  auto fill = [&](DecodeSideDev &d, const wtq_side_t &s) {
+    d.pages = (const uint8_t *)s.pages; d.norms = (const __half *)s.norms;
+    d.page_stride = s.page_stride; d.head_stride = s.head_stride;
+    d.norm_page_stride = s.norm_page_stride; d.norm_head_stride = s.norm_head_stride;
+    d.Pi = s.Pi; d.centroids = s.centroids; d.bw = s.bw; d.nb = D * s.bw / 8;
+  };
+  fill(p.k, *k_side);
+  fill(p.v, *v_side);
+  const size_t rows = (size_t)B * Q * Hq;
+  char *ws = (char *)workspace;
+  p.work_counter = (int32_t *)ws;
+  ws += 256;
+  p.row_lens = (int32_t *)ws;
+  ws += pf::round_up((size_t)B * Q * sizeof(int32_t), 256);
+  float *q_rot = (float *)ws;
+  ws += pf::round_up(rows * D * sizeof(float), 256);
+  p.part_acc = (float *)ws;
+  ws += pf::round_up(rows * splits * D * sizeof(float), 256);
+  p.part_m = (float *)ws;
+  ws += pf::round_up(rows * splits * sizeof(float), 256);
+  p.part_l = (float *)ws;
+  ws += pf::round_up(rows * splits * sizeof(float), 256);
+  p.lut = (const uint32_t *)ws;
+  p.q_rot = q_rot;
+  p.page_table = page_table; p.table_stride = table_stride; p.seq_lens = seq_lens;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.n_rep = Hq / Hkv; p.Q = Q; p.S = S; p.P = P;
+  p.max_pages = max_pages; p.max_tokens = max_tokens; p.num_splits = splits;
+  p.chunk_tokens = chunk_tokens;
+  p.row_blocks = (Q * p.n_rep + pf::kRows - 1) / pf::kRows;
+  p.status = status;
+  if ((int64_t)B * Hkv * p.row_blocks * splits > (int64_t)1 << 30)
+    return fail(WTQ_ERR_ARG, "wtq_prefill: too many work items; lower num_splits");
+
+  // what the tensor-core kernels need of the layout (the same as the decode scan)
+  DecodeParams probe = {};
+  probe.k = p.k; probe.v = p.v; probe.D = D; probe.S = S; probe.n_rep = p.n_rep;
+  probe.q_rot = q_rot; probe.part_acc = p.part_acc; probe.lut = p.lut;
+  if (!mma_eligible(probe) || D != 128)
+    return fail(WTQ_ERR_UNSUPPORTED, "wtq_prefill: needs head_dim 128, widths 4/4, 4/6, 6/6 or 8/8, "
+                "a power-of-two page size >= 16, at most 8 query heads per kv head and 16-byte "
+                "aligned pages");
+  if (cudaMemsetAsync(p.work_counter, 0, 256, stream) != cudaSuccess)
+    return check_cuda(cudaGetLastError(), "wtq_prefill: counter reset");
+  // rotation of the B * Q * Hq query rows (exp2 domain) and the lookup tables
+  ScanSetup setup = {nullptr, (uint32_t *)p.lut, k_side->centroids, v_side->centroids, k_side->bw,
+                     v_side->bw, mma_lut_words(k_side->bw, v_side->bw)};
+  if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, scale * 1.4426950408889634f, B * Q, Hq,
+                               D, q_rot, nullptr, chunk_tokens, max_tokens, setup, stream))
+    return rc;
+  int rc = WTQ_ERR_UNSUPPORTED;
+  if (p.k.bw == 4 && p.v.bw == 4) rc = pf::launch<4, 4>(p, stream);
+  else if (p.k.bw == 4 && p.v.bw == 6) rc = pf::launch<4, 6>(p, stream);
+  else if (p.k.bw == 6 && p.v.bw == 6) rc = pf::launch<6, 6>(p, stream);
+  else if (p.k.bw == 8 && p.v.bw == 8) rc = pf::launch<8, 8>(p, stream);
+  if (rc) return rc;
+  MergeParams m = {};
+  m.part_acc = p.part_acc; m.part_m = p.part_m; m.part_l = p.part_l;
+  m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
+  m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
+  m.work_counter = nullptr;
+  return launch_mma_merge(m, p.row_lens, B * Q, Hkv, p.n_rep, chunk_tokens, max_tokens, stream);
+}

@@ -224,8 +224,14 @@ def tiled_compressed_attention(q: torch.Tensor, kv: PackedKV, scale: float,
     for the stream, when the table comes from validated page references."""
     check_contract(q, kv, check_page_ids=check_page_ids)
     _require_cuda(q, "tiled_compressed_attention")
-    from .packed_attention_cuda import packed_decode_attention
+    from .packed_attention_cuda import (packed_decode_attention, packed_prefill_attention,
+                                        prefill_supported)
     B, Hq, Q, D = q.shape
+    if Q > 1 and prefill_supported(q, kv):
+        # one pass over the pages for the whole chunk (wtq_prefill)
+        splits = None if not split_pages else max(1, -(-kv.page_table.shape[1] // int(split_pages)))
+        return packed_prefill_attention(q.float(), kv, scale, num_splits=splits,
+                                        check_page_ids=False).contiguous()
     rows, view = _causal_rows(q.float(), kv)
     splits = None if not split_pages else max(1, -(-kv.page_table.shape[1] // int(split_pages)))
     out = packed_decode_attention(rows.contiguous(), view, scale, num_splits=splits,

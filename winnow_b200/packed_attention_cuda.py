@@ -184,6 +184,73 @@ def packed_decode_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
         return plan.run()
 
 
+_PREFILL_WS: dict = {}
+
+
+@torch.no_grad()
+def packed_prefill_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
+                             num_splits: int | None = None, check_page_ids: bool = True,
+                             status: torch.Tensor | None = None,
+                             workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of a chunk of Q query tokens per sequence over the
+    packed pages (`wtq_prefill`): q (B, Hq, Q, D) -> (B, Hq, Q, D) in q.dtype,
+    returned as a view of a (B, Q, Hq, D) tensor (the layout attention
+    interfaces hand back).  The chunk's own K/V must already be appended:
+    `kv.seq_lens` includes the Q tokens, and token i of the chunk sees keys
+    [0, seq_len - Q + i].  The pages are read and decoded once for all query
+    rows.  Raises `BackendError` (WTQ_ERR_UNSUPPORTED) for layouts only the
+    row-by-row decode path serves; `prefill_supported()` asks first."""
+    pa.check_contract(q, kv, check_page_ids=check_page_ids)
+    if not q.is_cuda:
+        raise pa.UnsupportedLayout("the CUDA prefill kernel needs CUDA tensors")
+    B, Hq, Q, D = q.shape
+    dev = q.device
+    Hkv, S, P = kv.num_kv_heads, kv.page_size, kv.k_pages.shape[0]
+    max_pages = kv.page_table.shape[1]
+    out = torch.empty(B, Q, Hq, D, dtype=q.dtype, device=dev)
+    if B == 0 or Q == 0:
+        return out.permute(0, 2, 1, 3)
+    if max_pages == 0:
+        return out.zero_().permute(0, 2, 1, 3)
+    rows = q.permute(0, 2, 1, 3).contiguous()                 # (B, Q, Hq, D): row b * Q + i
+    L = _lib.lib()
+    splits = int(num_splits or 0) or L.wtq_prefill_auto_splits(B, Hq, Hkv, Q, max_pages, S)
+    need = L.wtq_prefill_workspace_bytes(B, Hq, Hkv, Q, D, splits)
+    if workspace is None:
+        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+        workspace = _PREFILL_WS.get(key)
+        if workspace is None or workspace.numel() < need:
+            workspace = _PREFILL_WS[key] = torch.empty(need, dtype=torch.uint8, device=dev)
+    k_side = _side(kv.k_pages, kv.k_norms, kv.k_quant)
+    v_side = _side(kv.v_pages, kv.v_norms, kv.v_quant)
+    with torch.cuda.device(dev):
+        _lib.check(L.wtq_prefill(
+            rows.data_ptr(), _lib.dtype_code(q.dtype), _lib.i64x(Hq * D, D), out.data_ptr(),
+            _lib.i64x(Hq * D, D), ctypes.byref(k_side), ctypes.byref(v_side),
+            kv.page_table.data_ptr(), kv.page_table.stride(0), kv.seq_lens.data_ptr(), float(scale),
+            B, Hq, Hkv, Q, D, S, P, max_pages, splits, workspace.data_ptr(), workspace.numel(),
+            status.data_ptr() if status is not None else None,
+            torch.cuda.current_stream(dev).cuda_stream))
+    return out.permute(0, 2, 1, 3)
+
+
+def prefill_supported(q: torch.Tensor, kv: pa.PackedKV) -> bool:
+    """Whether `packed_prefill_attention` serves this layout (head_dim 128, a
+    width pair with a tensor-core kernel, power-of-two pages of at least 16
+    tokens, at most 8 query heads per kv head, 16-byte aligned pages)."""
+    D, S = kv.head_dim, kv.page_size
+    widths = (kv.k_quant.bit_width, kv.v_quant.bit_width)
+    ok = (q.is_cuda and D == 128 and widths in ((4, 4), (4, 6), (6, 6), (8, 8)) and S >= 16
+          and S & (S - 1) == 0 and q.shape[1] // kv.num_kv_heads <= 8
+          and q.dtype in (torch.float32, torch.float16, torch.bfloat16))
+    for pages, norms in ((kv.k_pages, kv.k_norms), (kv.v_pages, kv.v_norms)):
+        ok = ok and pages.data_ptr() % 16 == 0 and norms.data_ptr() % 16 == 0 \
+            and pages.stride(0) % 16 == 0 and pages.stride(1) % 16 == 0 \
+            and norms.stride(0) % 8 == 0 and norms.stride(1) % 8 == 0 \
+            and pages.stride(-1) == 1 and pages.stride(-2) == pages.shape[-1] and norms.stride(-1) == 1
+    return bool(ok and kv.page_table.stride(-1) == 1 and kv.seq_lens.is_contiguous())
+
+
 @torch.no_grad()
 def dense_decode_attention(q: torch.Tensor, kv: "pa.DenseKV", scale: float, *, num_splits: int = 1,
                            allow_tf32: bool = False, num_warps: int = 4, num_stages: int = 2,
