@@ -581,7 +581,8 @@ def time_prefill(w, handle, hq, scale, dev):
     not serve this layout."""
     from winnow_b200.packed_attention_cuda import packed_prefill_attention, prefill_supported
     g = torch.Generator().manual_seed(w.seed + 64)
-    q = torch.randn(w.batch, hq, PREFILL_Q, w.head_dim, generator=g).to(dev, w.dtype)
+    # queries drawn like the decode step's (workloads.queries): N(0, 1) / sqrt(head_dim)
+    q = (torch.randn(w.batch, hq, PREFILL_Q, w.head_dim, generator=g) * w.head_dim ** -0.5).to(dev, w.dtype)
     if not prefill_supported(q, handle):
         return None
     times = []
