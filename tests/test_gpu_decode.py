@@ -240,7 +240,7 @@ def test_attention_interface_entry_point():
     gq = torch.Generator().manual_seed(5)
     q5 = torch.randn(2, 8, 5, 128, generator=gq)
     out5, _ = pb.winnow_packed_attention(None, q5.to(DEV), kv, kv, None, scaling=0.09)
-    assert pb.BACKEND_COUNTS["prefill_reconstruct_sdpa"] == 1
+    assert pb.BACKEND_COUNTS["prefill_reconstruct_sdpa"] == 1      # a bare handle: the reference's path
     ref5 = orc.reconstruct_attention(q5, okv, 0.09)
     assert (out5.transpose(1, 2).cpu() - ref5).abs().max() < 2e-3
     kv.prefill_backend = "packed"        # additive: the chunk on the page-scan kernels

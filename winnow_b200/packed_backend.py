@@ -102,11 +102,14 @@ class PagedPackedCache:
     """
 
     def __init__(self, pool: PagePool, owners, lengths, *, k_quant, v_quant, head_dim: int,
-                 decode_backend: str = "auto", prefill_backend: str = "reconstruct"):
-        """`prefill_backend`: "reconstruct" (the reference's path: dequantize the
-        history, stock attention) or "packed" (additive: the chunk's queries run
-        on the page-scan kernels as one causal launch, no reconstruction)."""
-        if prefill_backend not in ("reconstruct", "packed"):
+                 decode_backend: str = "auto", prefill_backend: str = "auto"):
+        """`prefill_backend` (additive keyword): "packed" runs a chunk of query
+        tokens on the packed pages (the chunk kernel `wtq_prefill` where the
+        layout allows, B * Q decode rows otherwise: no reconstruction);
+        "reconstruct" is the reference's path (dequantize the history, stock
+        attention); "auto" picks "packed" where the chunk kernel serves the
+        layout and "reconstruct" elsewhere."""
+        if prefill_backend not in ("auto", "reconstruct", "packed"):
             raise ValueError(f"unknown prefill_backend {prefill_backend!r}")
         self.prefill_backend = prefill_backend
         self.pool = pool
@@ -338,6 +341,15 @@ def _dense_sdpa(query, kv: pa.DenseKV, scaling):
     return out
 
 
+def _prefill_choice(query, kv) -> str:
+    """ "packed" or "reconstruct" for a chunk of query tokens over `kv`."""
+    want = getattr(kv, "prefill_backend", "reconstruct")
+    if want != "auto":
+        return want
+    from .packed_attention_cuda import prefill_supported
+    return "packed" if prefill_supported(query, kv) else "reconstruct"
+
+
 def winnow_packed_attention(module, query, key, value, attention_mask, dropout: float = 0.0,
                             scaling=None, **kwargs):
     """`AttentionInterface` entry point.  Returns ((B, Q, Hq, D), None)."""
@@ -358,11 +370,15 @@ def winnow_packed_attention(module, query, key, value, attention_mask, dropout: 
             out = dense_decode_attention(query, key, scaling, num_splits=0)
         else:
             out = _dense_sdpa(query, key, scaling)
-    elif Q > 1 and getattr(key, "prefill_backend", "reconstruct") == "packed" and query.is_cuda:
+    elif Q > 1 and query.is_cuda and _prefill_choice(query, key) == "packed":
         BACKEND_COUNTS["prefill_cuda_packed"] += 1
-        out = pa.tiled_compressed_attention(
-            query, key, scaling,
-            check_page_ids=not getattr(key, "table_validated", False)).to(query.dtype)
+        from .packed_attention_cuda import packed_prefill_attention, prefill_supported
+        check = not getattr(key, "table_validated", False)
+        if prefill_supported(query, key):            # the chunk kernel, in the query's dtype
+            out = packed_prefill_attention(query, key, scaling, check_page_ids=check)
+        else:                                        # B * Q decode rows over the same pages
+            out = pa.tiled_compressed_attention(query, key, scaling,
+                                                check_page_ids=check).to(query.dtype)
     elif Q > 1:
         BACKEND_COUNTS["prefill_reconstruct_sdpa"] += 1
         out = _reconstruct_sdpa(query, key, scaling)
