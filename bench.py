@@ -216,6 +216,18 @@ def run_ours(args):
     rank, world, local = init_ranks(args.gpus)
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    if args.only != "all":
+        # one side measurement alone (what the ncu captures of those kernels run)
+        if world != 1:
+            raise SystemExit("--only dequant/prefill is a single-GPU measurement")
+        if args.only == "dequant":
+            print(json.dumps({"dequant": measure_dequant(dev)}))
+        else:
+            w = workloads.WORKLOADS[args.workload]
+            pool, handles, _ = build_gpu_cache(w, 0, 1, 1, dev)
+            us = time_prefill(w, handles[0], w.q_heads, w.head_dim ** -0.5, dev)
+            print(json.dumps({"prefill_us": us, "query_tokens": PREFILL_Q, "workload": workload_label(w)}))
+        return
     line = measure_workload(args.workload, args, rank, world, local, dev, main=True)
     extras = [] if args.extra in ("", "none") else [x for x in args.extra.split(",") if x]
     others = {}
@@ -503,7 +515,9 @@ def workload_label(w) -> str:
 # over its algorithmic bytes, from ncu captures of the named workloads (their
 # summaries are kept under profiles/; the excess over 1 is the chunk states the
 # kernel writes).  Other workloads and shards are scaled with the nearest entry.
-DRAM_TRAFFIC_RATIO = {("config2", 1): 145.5 / 138.7}
+DRAM_TRAFFIC_RATIO = {("config2", 1): (138.83 + 3.82) / 138.71,
+                      ("config5", 1): (1114.06 + 23.03) / 1110.3,
+                      ("headline32k", 1): (554.22 + 10.65) / 554.0}
 
 
 def dram_traffic_ratio(name: str, world: int):
@@ -690,6 +704,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config2", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--only", default="all", choices=["all", "dequant", "prefill"],
+                    help="run just the dequantisation or the prefill measurement (single GPU)")
     ap.add_argument("--dequant", type=int, default=1,
                     help="1: also time the fused dequantisation kernels (single GPU only)")
     ap.add_argument("--extra", default="headline32k,config3,config4,config5",

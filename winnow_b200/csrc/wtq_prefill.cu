@@ -266,48 +266,70 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
     }
 
     // ---- copy of one tile into a landing buffer ----------------------------------
+    // Done in two steps so that the page-table reads are not in front of the
+    // copies: `lookup(j)` fetches the page id of each of this thread's pieces of
+    // tile j into registers (at the top of tile j - 1's turn), `copy(j)` issues
+    // the copies after that tile has been decoded.
     const int32_t *table = p.page_table + (int64_t)b * p.table_stride;
-    auto issue = [&](int j) {
-      const uint32_t raw = M::kRaw + (uint32_t)(j & 1) * M::kRawBytes;
-      const int tok0 = start + j * kTile;
-      constexpr int kPiecesK = kTile * M::kNBK / 16, kPiecesV = kTile * M::kNBV / 16;
-      constexpr int kPieces = kPiecesK + kPiecesV + 16;     // + 8 + 8 pieces of norms
-      for (int c = tid; c < kPieces; c += kThreads) {
-        int side, tok, off;                                  // side 0/1: codes, 2/3: norms
+    constexpr int kPiecesK = kTile * M::kNBK / 16, kPiecesV = kTile * M::kNBV / 16;
+    constexpr int kPieces = kPiecesK + kPiecesV + 16;       // + 8 + 8 pieces of norms
+    constexpr int kTurns = (kPieces + kThreads - 1) / kThreads;
+    // piece c: side 0/1 = K/V codes, 2/3 = K/V norms; first token; byte offset in the row
+    auto piece = [&](int c, int &side, int &tok, int &off, uint32_t &dst) {
+      if (c < kPiecesK) {
+        side = 0; tok = c / (M::kNBK / 16); off = (c - tok * (M::kNBK / 16)) * 16; dst = 16u * c;
+      } else if (c < kPiecesK + kPiecesV) {
+        const int cc = c - kPiecesK;
+        side = 1; tok = cc / (M::kNBV / 16); off = (cc - tok * (M::kNBV / 16)) * 16;
+        dst = M::kRawV + 16u * cc;
+      } else {
+        const int cc = c - kPiecesK - kPiecesV;              // eight tokens of norms per piece
+        side = 2 + (cc >> 3); tok = (cc & 7) * 8; off = 0;
+        dst = (side == 2 ? M::kRawNK : M::kRawNV) + 16u * (cc & 7);
+      }
+    };
+    int page_of[kTurns];                                     // -2: the piece lies past the end
+    auto lookup = [&](int j) {
+#pragma unroll
+      for (int i = 0; i < kTurns; ++i) {
+        const int c = tid + i * kThreads;
+        int side, tok, off;
         uint32_t dst;
-        if (c < kPiecesK) {
-          side = 0; tok = c / (M::kNBK / 16); off = (c - tok * (M::kNBK / 16)) * 16; dst = raw + 16u * c;
-        } else if (c < kPiecesK + kPiecesV) {
-          const int cc = c - kPiecesK;
-          side = 1; tok = cc / (M::kNBV / 16); off = (cc - tok * (M::kNBV / 16)) * 16;
-          dst = raw + M::kRawV + 16u * cc;
-        } else {
-          const int cc = c - kPiecesK - kPiecesV;            // eight tokens of norms per piece
-          side = 2 + (cc >> 3); tok = (cc & 7) * 8; off = 0;
-          dst = raw + (side == 2 ? M::kRawNK : M::kRawNV) + 16u * (cc & 7);
-        }
-        const int token = tok0 + tok;
-        int bytes = token < end ? 16 : 0;
+        piece(c < kPieces ? c : 0, side, tok, off, dst);
+        const int token = start + j * kTile + tok;
+        page_of[i] = c < kPieces && token < end ? table[token >> page_shift] : -2;
+      }
+    };
+    auto copy = [&](int j) {
+      const uint32_t raw = M::kRaw + (uint32_t)(j & 1) * M::kRawBytes;
+#pragma unroll
+      for (int i = 0; i < kTurns; ++i) {
+        const int c = tid + i * kThreads;
+        if (c >= kPieces) break;
+        int side, tok, off;
+        uint32_t dst;
+        piece(c, side, tok, off, dst);
+        const int page = page_of[i], pos = (start + j * kTile + tok) & (p.S - 1);
+        int bytes = 16;
         const void *src = p.k.pages;                         // any valid address when nothing is read
-        if (bytes) {
-          const int page = table[token >> page_shift], pos = token & (p.S - 1);
-          if (page < 0 || page >= p.P) {
-            if (p.status) atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
-            bytes = 0;
-          } else if (side < 2) {
-            const DecodeSideDev &sd = side ? p.v : p.k;
-            src = sd.pages + (int64_t)page * sd.page_stride + (int64_t)kvh * sd.head_stride +
-                  (int64_t)pos * sd.nb + off;
-          } else {
-            const DecodeSideDev &sd = side == 3 ? p.v : p.k;
-            src = sd.norms + (int64_t)page * sd.norm_page_stride + (int64_t)kvh * sd.norm_head_stride + pos;
-          }
+        if (page < 0 || page >= p.P) {
+          if (page != -2 && p.status) atomicOr(p.status, WTQ_STATUS_BAD_PAGE);
+          bytes = 0;
+        } else if (side < 2) {
+          const DecodeSideDev &sd = side ? p.v : p.k;
+          src = sd.pages + (int64_t)page * sd.page_stride + (int64_t)kvh * sd.head_stride +
+                (int64_t)pos * sd.nb + off;
+        } else {
+          const DecodeSideDev &sd = side == 3 ? p.v : p.k;
+          src = sd.norms + (int64_t)page * sd.norm_page_stride + (int64_t)kvh * sd.norm_head_stride + pos;
         }
-        copy16(dst, src, bytes);
+        copy16(raw + dst, src, bytes);
       }
       asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
-    issue(0);
+    lookup(0);
+    copy(0);
+    if (ntiles > 1) lookup(1);
 
     float o[2][16][4];                                      // rows x coordinates of the value basis
     float mx[2][2], sum[2][2];
@@ -345,7 +367,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
         }
       }
       __syncthreads();
-      if (j + 1 < ntiles) issue(j + 1);
+      if (j + 1 < ntiles) copy(j + 1);
+      if (j + 2 < ntiles) lookup(j + 2);                    // ids for the tile after: a whole tile ahead
       if (!warp_on || tok0 >= warp_hi) continue;            // no row of this warp sees the tile
 
       // ---- scores -------------------------------------------------------------------
