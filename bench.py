@@ -62,7 +62,13 @@ class ClockSampler:
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-i", str(self.index), "-lms", "100"], stdout=fd, stderr=subprocess.DEVNULL)
             os.close(fd)
-            time.sleep(0.25)
+            # wait for the first sample: the tool's start-up (it attaches to every GPU
+            # of the box) must be over before the timed region begins, or it can
+            # stall launches inside a region that lasts only a few milliseconds
+            deadline = time.time() + 5.0
+            while time.time() < deadline and os.path.getsize(self.path) == 0:
+                time.sleep(0.02)
+            time.sleep(0.1)
         except Exception:                                   # noqa: BLE001
             self.proc = None
         return self
@@ -388,11 +394,21 @@ def measure_workload(name, args, rank, world, local, dev, main):
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
+        barrier(world)                                       # every rank's sampler is up
         start.record()
         for i in range(steps):
             step(args.warmup + i)
         end.record()
         barrier(world)
+        # the same K steps once more: a figure far from `value` means one of the two
+        # regions was disturbed (they last only K x a few tens of microseconds)
+        s1, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s1.record()
+        for i in range(steps):
+            step(args.warmup + i)
+        e1.record()
+        barrier(world)
+        repeat_ms = max_over_ranks(s1.elapsed_time(e1) / steps, world, dev)
         steady_ms = None
         if main and steps < 200:
             # the same measurement over 200 steps (the K above may be a handful)
@@ -466,7 +482,7 @@ def measure_workload(name, args, rank, world, local, dev, main):
                 "kernel": "page-scan kernel of wtq_decode", "kernel_us": kernel_us,
                 "algorithmic_bytes_per_launch": alg_rank}
     if not main:
-        return {"step_us": ms * 1e3, "steps": steps, "e2e_us": e2e_ms * 1e3, "append_us": append_us,
+        return {"step_us": ms * 1e3, "repeat_us": repeat_ms * 1e3, "steps": steps, "e2e_us": e2e_ms * 1e3, "append_us": append_us,
                 "hbm_gbs": alg_total / (ms * 1e-3) / 1e9, "roofline": roofline,
                 "config": workload_label(w), "layers_rotated": layers,
                 "parity_max_abs_err_vs_oracle": parity,
@@ -482,6 +498,7 @@ def measure_workload(name, args, rank, world, local, dev, main):
                    "num_splits": args.splits or "auto", "exchange": exchange_note,
                    "launch": "cuda graph replay" if args.graph else "pre-marshalled call"},
         "steady_us_over_200_steps": None if steady_ms is None else steady_ms * 1e3,
+        "repeat_us": repeat_ms * 1e3,
         "hbm_gbs": alg_total / (ms * 1e-3) / 1e9,
         "hbm_frac_of_8tbs_nominal": alg_total / (ms * 1e-3) / 1e9 / (NOMINAL_HBM_GBS * world),
         "tokens_per_s": w.batch / (ms * 1e-3),
