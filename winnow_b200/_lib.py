@@ -107,7 +107,7 @@ def exported_symbols() -> list[str]:
 def lib():
     global _lib
     if _lib is None:
-        path = os.environ.get("WTQ_LIB_PATH", str(LIB))   # development aid: an alternative build
+        path = str(LIB)
         if not os.path.exists(path):
             raise BackendError(
                 f"{LIB} is not built; run `python -c \"import __graft_entry__ as g; g.build()\"` "
