@@ -106,6 +106,19 @@ def test_full_chunk_of_a_long_history():
     _check(q, okv)
 
 
+@pytest.mark.parametrize("dtype,splits", [(torch.float32, 5), (torch.bfloat16, 8), (torch.float16, None),
+                                          (torch.float32, 10)])
+def test_many_rows_rotate_and_merge_on_the_tensor_cores(dtype, splits):
+    """5120 query rows: the rotation and (up to 8 chunks per row) the merge of
+    the call run as tensor-core kernels; with 10 chunks the merge falls back to
+    the decode path's kernel.  Same answers either way."""
+    q, okv = _case(720 + (splits or 0), 2, 32, 8, (2700, 300), 16, 4, 4, 80)
+    if dtype == torch.float32:
+        _check(q, okv, splits=splits)
+    else:
+        _check(q, okv, splits=splits, dtype=dtype, atol=2e-2, rel_l2=1e-2)
+
+
 def test_tiled_compressed_attention_uses_the_chunk_kernel():
     """The operator of the reference's name routes chunks to wtq_prefill where
     the layout allows and to B * Q decode rows where it does not."""

@@ -88,6 +88,17 @@ int mma_chunk_tokens(int max_tokens, int splits);
 int launch_decode_mma(const DecodeParams &p, const MergeParams &m, cudaStream_t stream);
 int launch_mma_merge(const MergeParams &m, const int32_t *seq_lens, int B, int Hkv, int n_rep,
                      int chunk_tokens, int max_tokens, cudaStream_t stream);
+// Tensor-core forms of the query rotation and of the chunk merge for calls with
+// thousands of rows (wtq_rows_mma.cu); the *_eligible functions say whether a
+// call qualifies (contiguous rows of 128, at least 4096 of them, 16-byte aligned
+// buffers; the merge also: at most 8 chunks per row, no exchange).
+bool rows_mma_rotate_eligible(const void *q, int64_t row_stride, int64_t head_stride, int Hq, int D,
+                              int64_t rows, const float *Pi, const float *q_rot);
+int launch_rotate_rows_mma(const void *q, int dtype, const float *Pi, float mult, int64_t rows,
+                           float *q_rot, const ScanSetup &setup, int32_t *status, cudaStream_t stream);
+bool rows_mma_merge_eligible(const MergeParams &m, int64_t rows);
+int launch_merge_rows_mma(const MergeParams &m, const int32_t *row_lens, int64_t rows, int chunk_tokens,
+                          int max_tokens, int32_t *status, cudaStream_t stream);
 int launch_exchange_wait(const uint32_t *flags, int world, uint32_t *state, long long spin_limit,
                          int32_t *status, cudaStream_t stream);
 

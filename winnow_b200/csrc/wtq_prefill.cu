@@ -684,9 +684,16 @@ extern "C" int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2],
   // rotation of the B * Q * Hq query rows (exp2 domain) and the lookup tables
   ScanSetup setup = {nullptr, (uint32_t *)p.lut, k_side->centroids, v_side->centroids, k_side->bw,
                      v_side->bw, mma_lut_words(k_side->bw, v_side->bw)};
-  if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, scale * 1.4426950408889634f, B * Q, Hq,
-                               D, q_rot, nullptr, chunk_tokens, max_tokens, setup, stream))
+  const float q_scale = scale * 1.4426950408889634f;
+  const int64_t total_rows = (int64_t)B * Q * Hq;
+  if (rows_mma_rotate_eligible(q, q_strides[0], q_strides[1], Hq, D, total_rows, k_side->Pi, q_rot)) {
+    if (int rc = launch_rotate_rows_mma(q, dtype, k_side->Pi, q_scale, total_rows, q_rot, setup, status,
+                                        stream))
+      return rc;
+  } else if (int rc = launch_rotate_q(q, dtype, q_strides, k_side->Pi, q_scale, B * Q, Hq, D, q_rot,
+                                      nullptr, chunk_tokens, max_tokens, setup, stream)) {
     return rc;
+  }
   int rc = WTQ_ERR_UNSUPPORTED;
   if (p.k.bw == 4 && p.v.bw == 4) rc = pf::launch<4, 4>(p, stream);
   else if (p.k.bw == 4 && p.v.bw == 6) rc = pf::launch<4, 6>(p, stream);
@@ -698,5 +705,7 @@ extern "C" int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2],
   m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
   m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
   m.work_counter = nullptr;
+  if (rows_mma_merge_eligible(m, total_rows))
+    return launch_merge_rows_mma(m, p.row_lens, total_rows, chunk_tokens, max_tokens, status, stream);
   return launch_mma_merge(m, p.row_lens, B * Q, Hkv, p.n_rep, chunk_tokens, max_tokens, stream);
 }
