@@ -495,22 +495,28 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
         nv[n][0] = v.x; nv[n][1] = v.y;
       }
       uint32_t pa[2][8][2];                                  // P * value norm as fp16 pairs
+      float base[2][2];
 #pragma unroll
-      for (int m = 0; m < 2; ++m) {
-        const float base0 = mx[m][0] == -INFINITY ? 0.f : mx[m][0];
-        const float base1 = mx[m][1] == -INFINITY ? 0.f : mx[m][1];
+      for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const float p0 = ex2(s[m][n][0] - base0), p1 = ex2(s[m][n][1] - base0);
-          const float p2 = ex2(s[m][n][2] - base1), p3 = ex2(s[m][n][3] - base1);
+        for (int h = 0; h < 2; ++h) base[m][h] = mx[m][h] == -INFINITY ? 0.f : mx[m][h];
+      auto probabilities = [&](int n) {                      // of tokens 8 n .. 8 n + 7
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          const float p0 = ex2(s[m][n][0] - base[m][0]), p1 = ex2(s[m][n][1] - base[m][0]);
+          const float p2 = ex2(s[m][n][2] - base[m][1]), p3 = ex2(s[m][n][3] - base[m][1]);
           sum[m][0] += p0 + p1;
           sum[m][1] += p2 + p3;
           pa[m][n][0] = pack_half2(p0 * nv[n][0], p1 * nv[n][1]);    // every norm in the tile is finite
           pa[m][n][1] = pack_half2(p2 * nv[n][0], p3 * nv[n][1]);
         }
-      }
+      };
 
-      // ---- values ---------------------------------------------------------------------
+      // ---- values: in source order the probabilities of the next 16 tokens sit
+      // between the MMAs of the current 16 (the compiler is free to schedule the
+      // exponentials under the tensor pipe's work; measured, it made no difference)
+      probabilities(0);
+      probabilities(1);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
 #pragma unroll
@@ -524,6 +530,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
             mma16816_free(o[m][2 * dp + 1], pa[m][2 * kk][0], pa[m][2 * kk][1], pa[m][2 * kk + 1][0],
                      pa[m][2 * kk + 1][1], vb[2], vb[3]);
           }
+          if (kk < 3 && dp == 1) probabilities(2 * kk + 2);
+          if (kk < 3 && dp == 5) probabilities(2 * kk + 3);
         }
       }
     }
