@@ -576,11 +576,13 @@ def measure_dequant(dev) -> dict:
     nbytes = rows * (64 + 2 + 256)
     peak, kind = measured_peak()
     result = {"rows": rows, "bits": 4, "out_dtype": "bf16", "bytes_per_call": nbytes, "us": {}, "gbs": {},
-              "modes": {"tc": "tensor cores, fp16 high/low split operands (what bf16/fp16 outputs get "
-                              "by default)",
-                        "tc_fast": "tensor cores, single fp16 operands (the reference's allow_tf32 class)",
+              "modes": {"tc": "tcgen05 (accumulator in tensor memory), fp16 high/low split operands: what "
+                              "bf16/fp16 outputs get by default",
+                        "tc_fast": "tcgen05, single fp16 operands (the reference's allow_tf32 class)",
+                        "tc_mma": "the split form on mma.sync (the fallback of tc)",
+                        "tc_fast_mma": "the single form on mma.sync (the fallback of tc_fast)",
                         "exact": "fp32 on the CUDA cores"}}
-    for mode, reps in (("tc", 20), ("tc_fast", 20), ("exact", 3)):
+    for mode, reps in (("tc", 20), ("tc_fast", 20), ("tc_mma", 20), ("tc_fast_mma", 20), ("exact", 3)):
         out = torch.empty(rows, 128, dtype=torch.bfloat16, device=dev)
         for _ in range(3):
             dequantize_rows(packed, norms, tq.centroids, tq.Pi, 4, 128, out=out, mode=mode)
@@ -597,7 +599,7 @@ def measure_dequant(dev) -> dict:
     exact = outs["exact"].float()
     top = float(exact.abs().max())
     result["max_abs_diff_vs_exact_over_max"] = {m: float((outs[m].float() - exact).abs().max()) / top
-                                                for m in ("tc", "tc_fast")}
+                                                for m in ("tc", "tc_fast", "tc_mma", "tc_fast_mma")}
     result["frac_of_hbm_peak"] = result["gbs"]["tc"] / peak
     result["peak_kind"] = kind
     return result

@@ -273,6 +273,10 @@ int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2], void *out,
 #define WTQ_DEQUANT_EXACT 0
 #define WTQ_DEQUANT_TC 1
 #define WTQ_DEQUANT_TC_FAST 2
+/* the same two with the mma.sync kernels named explicitly (TC and TC_FAST run the
+ * tcgen05 kernel, accumulator in tensor memory, and fall back to these) */
+#define WTQ_DEQUANT_TC_MMA 3
+#define WTQ_DEQUANT_TC_FAST_MMA 4
 int wtq_dequant(const uint8_t *packed, const void *norms_f16, const float *centroids,
                 const float *Pi, void *out, int out_dtype, int bw, int D, int64_t N, int64_t L,
                 int64_t MAXLEN, void *stream);

@@ -175,7 +175,7 @@ def test_dequant_strided_cache_slice():
 
 @pytest.mark.parametrize("bw", [4, 6, 8])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("mode", ["tc", "tc_fast"])
+@pytest.mark.parametrize("mode", ["tc", "tc_fast", "tc_mma", "tc_fast_mma"])
 def test_dequant_tensor_core_modes(bw, dtype, mode):
     """Tensor-core dequantisation against the oracle on rows that end inside a
     32-row tile and planes (L = 27 of MAXLEN = 40) that end inside one: "tc"
@@ -199,7 +199,7 @@ def test_dequant_tensor_core_modes(bw, dtype, mode):
                               o.centroids, o.Pi, bw, 128)
     got = out.float().cpu()
     top = float(ref.abs().max())
-    if mode == "tc_fast":
+    if mode.startswith("tc_fast"):
         assert float((got - ref).abs().max()) <= 2.0 ** -9 * top + (0 if dtype == torch.float32 else 2.0 ** -8 * top)
         return
     if dtype == torch.float32:

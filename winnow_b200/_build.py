@@ -9,7 +9,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libwinnow_tq.so"
-SOURCES = ["wtq_pack.cu", "wtq_append.cu", "wtq_decode.cu", "wtq_decode_mma.cu", "wtq_api.cu", "wtq_dequant.cu", "wtq_prefill.cu", "wtq_rows_mma.cu",
+SOURCES = ["wtq_pack.cu", "wtq_append.cu", "wtq_decode.cu", "wtq_decode_mma.cu", "wtq_api.cu", "wtq_dequant.cu", "wtq_dequant_umma.cu", "wtq_prefill.cu", "wtq_rows_mma.cu",
            "wtq_decode_static.cu", "wtq_dense.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]

@@ -15,6 +15,7 @@ ORDER_AUTO, ORDER_SEQUENTIAL, ORDER_INTERLEAVED16 = -1, 0, 1
 STATUS_BAD_PAGE, STATUS_BAD_POSITION = 1, 2
 STATUS_LAYOUT, STATUS_SCAN_TIMEOUT = 8, 16
 DEQUANT_AUTO, DEQUANT_EXACT, DEQUANT_TC, DEQUANT_TC_FAST = -1, 0, 1, 2
+DEQUANT_TC_MMA, DEQUANT_TC_FAST_MMA = 3, 4
 
 _DTYPES = {torch.float32: WTQ_F32, torch.float16: WTQ_F16, torch.bfloat16: WTQ_BF16}
 

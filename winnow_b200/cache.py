@@ -109,7 +109,9 @@ def dequantize_rows(packed: torch.Tensor, norms: torch.Tensor, centroids: torch.
     Arithmetic (`mode`): "exact" is an fp32 contraction on the CUDA cores; "tc"
     runs on the tensor cores with centroids and Pi split into fp16 high and low
     parts (three products, fp32 accumulation); "tc_fast" uses single fp16
-    operands, the accuracy class of the reference's `allow_tf32=True`.  With
+    operands, the accuracy class of the reference's `allow_tf32=True`; both run
+    the tcgen05 kernel (accumulator in tensor memory), "tc_mma" / "tc_fast_mma"
+    name the mma.sync kernels they fall back to.  With
     `mode=None`: `allow_tf32=True` asks for "tc_fast" where the tensor-core
     kernel applies (head_dim 128, widths 4/6/8), otherwise the library picks
     "tc" for 16-bit outputs it applies to and "exact" for everything else.
@@ -119,8 +121,8 @@ def dequantize_rows(packed: torch.Tensor, norms: torch.Tensor, centroids: torch.
         if allow_tf32 and head_dim == 128 and bit_width in (4, 6, 8):
             code = _lib.DEQUANT_TC_FAST
     else:
-        code = {"exact": _lib.DEQUANT_EXACT, "tc": _lib.DEQUANT_TC,
-                "tc_fast": _lib.DEQUANT_TC_FAST}[mode]
+        code = {"exact": _lib.DEQUANT_EXACT, "tc": _lib.DEQUANT_TC, "tc_fast": _lib.DEQUANT_TC_FAST,
+                "tc_mma": _lib.DEQUANT_TC_MMA, "tc_fast_mma": _lib.DEQUANT_TC_FAST_MMA}[mode]
     dev = _lib.require_cuda(packed, norms, centroids, Pi)
     nb = packed_bytes(head_dim, bit_width)
     if packed.dtype != torch.uint8 or packed.shape[-1] != nb:

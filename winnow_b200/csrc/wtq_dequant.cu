@@ -25,6 +25,7 @@
 // significant products are accumulated in fp32.
 #include "wtq_common.cuh"
 #include "wtq_lut.cuh"
+#include "wtq_dequant.cuh"
 
 #include <atomic>
 #include <mutex>
@@ -32,15 +33,6 @@
 namespace wtq {
 
 constexpr int kRows = 16;
-
-struct DequantParams {
-  const uint8_t *packed;
-  const __half *norms;
-  const float *centroids, *Pi;
-  void *out;
-  int out_dtype, bw, D, nb;
-  int64_t N, L, MAXLEN;
-};
 
 __global__ void dequant_kernel(DequantParams p) {
   __shared__ float y[kRows][256];
@@ -528,7 +520,7 @@ extern "C" int wtq_dequant_mode(const uint8_t *packed, const void *norms_f16, co
     return fail(WTQ_ERR_ARG, "wtq_dequant: bit width %d unsupported for D=%d", bw, D);
   if (out_dtype < WTQ_F32 || out_dtype > WTQ_BF16)
     return fail(WTQ_ERR_ARG, "wtq_dequant: bad output dtype");
-  if (mode < WTQ_DEQUANT_AUTO || mode > WTQ_DEQUANT_TC_FAST)
+  if (mode < WTQ_DEQUANT_AUTO || mode > WTQ_DEQUANT_TC_FAST_MMA)
     return fail(WTQ_ERR_ARG, "wtq_dequant: bad mode %d", mode);
   if (N == 0) return WTQ_OK;
   if (L < 1 || MAXLEN < L) return fail(WTQ_ERR_ARG, "wtq_dequant: need 1 <= L <= MAXLEN");
@@ -540,19 +532,31 @@ extern "C" int wtq_dequant_mode(const uint8_t *packed, const void *norms_f16, co
   p.N = N; p.L = L; p.MAXLEN = MAXLEN;
   const char *why = nullptr;
   const bool can = mma_eligible(p, &why);
+  // Tensor-core modes: the tcgen05 kernel where it can run, the mma.sync kernel
+  // otherwise (or when asked for by name).
+  auto tensor_cores = [&](int terms, bool legacy_only, bool *unavailable) -> int {
+    if (!legacy_only) {
+      bool usable = false;
+      if (int rc = launch_dequant_umma(p, terms, stream, &usable)) return rc;
+      if (usable) return WTQ_OK;
+    }
+    return terms == 3 ? launch_mma_width<3>(p, stream, unavailable)
+                      : launch_mma_width<1>(p, stream, unavailable);
+  };
   if (mode == WTQ_DEQUANT_AUTO) {
-    // 16-bit outputs take the split tensor-core kernel where it applies; fp32
+    // 16-bit outputs take the split tensor-core form where it applies; fp32
     // outputs keep the fp32 contraction.
     if (!can || out_dtype == WTQ_F32) return launch_exact(p, stream);
     bool unavailable = false;
-    const int rc = launch_mma_width<3>(p, stream, &unavailable);
+    const int rc = tensor_cores(3, false, &unavailable);
     return unavailable ? launch_exact(p, stream) : rc;
   }
   if (mode == WTQ_DEQUANT_EXACT) return launch_exact(p, stream);
   if (!can) return fail(WTQ_ERR_UNSUPPORTED, "wtq_dequant: tensor-core kernel: %s", why);
   bool unavailable = false;
-  return mode == WTQ_DEQUANT_TC ? launch_mma_width<3>(p, stream, &unavailable)
-                                : launch_mma_width<1>(p, stream, &unavailable);
+  const bool split = mode == WTQ_DEQUANT_TC || mode == WTQ_DEQUANT_TC_MMA;
+  const bool legacy = mode == WTQ_DEQUANT_TC_MMA || mode == WTQ_DEQUANT_TC_FAST_MMA;
+  return tensor_cores(split ? 3 : 1, legacy, &unavailable);
 }
 
 extern "C" int wtq_dequant(const uint8_t *packed, const void *norms_f16, const float *centroids,

@@ -152,7 +152,7 @@ class PeerExchange:
     def check(self) -> None:
         """Raise if any wait since the last check gave up (synchronises with
         the device: call it where the caller syncs anyway, e.g. before sampling).
-        The status word is cleared so that later steps are judged on their own."""
+        The status word is cleared so that later steps are assessed on their own."""
         from . import _lib
         word = int(self.status.item())
         if word:
