@@ -3,8 +3,8 @@
 // widths 4/6/8, with the 128 x 128 accumulator of a tile in tensor memory
 // instead of registers.
 //
-// A block of eight warps takes tiles of 128 packed rows.  Per tile:
-//   decode    every warp turns 16 rows into fp16 centroid values through the
+// A block of sixteen warps takes tiles of 128 packed rows.  Per tile:
+//   decode    every warp turns 8 rows into fp16 centroid values through the
 //             per-lane lookup tables (wtq_lut.cuh) and stores them as the A
 //             operand in shared memory, in the canonical K-major layout without
 //             swizzle: 8-row x 16-byte core matrices, 128 bytes each, the 16
@@ -13,9 +13,9 @@
 //             out) for the eight K steps of each product term; B is Pi with one
 //             row per output coordinate in the same layout, resident in shared
 //             memory; tcgen05.commit signals an mbarrier when they are done;
-//   store     every warp reads its 32 lanes x 64 columns of the accumulator with
-//             tcgen05.ld, scales by the row norm, converts and writes 128 (256
-//             for fp32) contiguous bytes per row.
+//   store     every warp reads its 32 lanes x 32 columns of the accumulator with
+//             tcgen05.ld, scales by the row norm, converts, and passes the rows
+//             through a staging area so that they leave as whole row segments.
 // The accumulator is double-buffered: while the tensor cores work on tile i the
 // warps store tile i - 1, and the packed rows of tile i + 1 are already on their
 // way into registers.
@@ -33,7 +33,9 @@
 namespace wtq {
 namespace dq5 {
 
-constexpr int kWarps = 8, kThreads = 32 * kWarps;
+constexpr int kWarps = 16, kThreads = 32 * kWarps;
+constexpr int kLaneRows = 16 / kWarps;             // rows a lane decodes per tile (8 per warp each)
+constexpr int kWarpCols = 128 / (kWarps / 4);      // accumulator columns a warp stores
 constexpr uint32_t kBase = 1024;                  // dynamic shared memory is assumed to start at or below this
 constexpr uint32_t kBar = kBase;                  // mbarrier (8 bytes)
 constexpr uint32_t kTmemSlot = kBase + 16;        // tensor-memory address written by tcgen05.alloc
@@ -43,8 +45,8 @@ constexpr uint32_t kOperand = 128 * 128 * 2;      // one fp16 operand tile
 constexpr uint32_t kBHi = 4096;
 static_assert(kCent + 1024 <= kBHi, "low region");
 constexpr uint32_t kStage = kBHi + kOperand;      // output staging, per warp (see store_tile)
-constexpr uint32_t kStageBytes = 16 * (128 + 16);
-static_assert(kStage + kWarps * kStageBytes <= mma::kLutAddr && 8 * (256 + 16) <= kStageBytes, "staging");
+constexpr uint32_t kStageBytes = 16 * (2 * kWarpCols + 16);
+static_assert(kStage + kWarps * kStageBytes <= mma::kLutAddr && 8 * (4 * kWarpCols + 16) <= kStageBytes, "staging");
 constexpr uint32_t kCols = 256;                   // tensor memory: two accumulators of 128 columns
 constexpr float kOperandScale = 256.f, kResultScale = 1.f / (256.f * 256.f);
 // instruction descriptor: dense, fp32 accumulator, fp16 A and B, both K-major, N = 128, M = 128
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
   // B[c][d] = Pi[d][c]: a lane takes column c = 8 cb + (lane & 7) and the rows d = 2 (4 db +
   // (lane >> 3)), d + 1 (sector-sized reads)
 #pragma unroll 8
-  for (int it = 0; it < 32; ++it) {
+  for (int it = 0; it < 256 / kWarps; ++it) {
     const int combo = it * kWarps + warp, cb = combo & 15, db = combo >> 4;
     const int c = 8 * cb + (lane & 7), d = 2 * (4 * db + (lane >> 3));
     const float x0 = __ldg(p.Pi + d * 128 + c) * kOperandScale;
@@ -211,9 +213,9 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
   uint32_t phase = 0;
   bool gave_up = false;
 
-  // packed words and norm of the lane's two rows (16 warp + g, + 8) of a tile
+  // packed words and norm of the lane's row(s) of a tile
   const bool dense = p.L == p.MAXLEN;                       // source row = logical row: no plane arithmetic
-  auto fetch = [&](int64_t tile, uint32_t (&w)[2][BW], float (&nrm)[2]) {
+  auto fetch = [&](int64_t tile, uint32_t (&w)[kLaneRows][BW], float (&nrm)[kLaneRows]) {
     const int64_t row0 = tile << 7;
     const int last = (int)min((int64_t)127, p.N - 1 - row0);   // rows past the end re-read the last one
     int64_t plane0 = 0;
@@ -223,8 +225,8 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
       pos0 = (uint32_t)(row0 - plane0 * p.L);
     }
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int lr = min(16 * warp + 8 * h + g, last);
+    for (int h = 0; h < kLaneRows; ++h) {
+      const int lr = min(8 * kLaneRows * warp + 8 * h + g, last);
       int64_t src = row0 + lr;
       if (!dense) {
         const uint32_t pos = pos0 + (uint32_t)lr, wrap = pos / L32;
@@ -234,34 +236,34 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
       nrm[h] = __half2float(p.norms[src]) * kResultScale;
     }
   };
-  // this thread's share of a finished accumulator: lane 32 (warp % 4) + lane, columns 64 (warp / 4) ..
+  // this thread's share of a finished accumulator: lane 32 (warp % 4) + lane, columns
+  // kWarpCols (warp / 4) ..
   auto store_tile = [&](int64_t tile, int buf) {
     const int lr = 32 * (warp & 3) + lane;
     const float nrm = __uint_as_float(lds32(kNorms + 512u * buf + 4u * lr));
-    const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(128 * buf + 64 * (warp >> 2));
-    uint32_t v0[32], v1[32];
-    tmem_load32(taddr, v0);
-    tmem_load32(taddr + 32, v1);
+    const uint32_t taddr =
+        tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(128 * buf + kWarpCols * (warp >> 2));
+    uint32_t v[kWarpCols / 32][32];
+#pragma unroll
+    for (int i = 0; i < kWarpCols / 32; ++i) tmem_load32(taddr + 32 * i, v[i]);
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-    // The thread holds 64 consecutive columns of ONE row; stored as they are, every
+    // The thread holds consecutive columns of ONE row; stored as they are, every
     // store instruction of the warp would touch 32 rows.  A few rows at a time go
     // through a staging area instead and leave as whole row segments.
-    constexpr int kRowBytes = 64 * kEsize;                  // this warp's part of a row
+    constexpr int kRowBytes = kWarpCols * kEsize;           // this warp's part of a row
     constexpr int kPassRows = kEsize == 2 ? 16 : 8;
     constexpr uint32_t kStride = kRowBytes + 16;            // pad: the rows of a pass land in different banks
     const uint32_t stage = kStage + (uint32_t)warp * kStageBytes;
     uint32_t q[kRowBytes / 4];                              // the row segment, converted
-    if constexpr (kEsize == 4) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        q[i] = __float_as_uint(__uint_as_float(v0[i]) * nrm);
-        q[32 + i] = __float_as_uint(__uint_as_float(v1[i]) * nrm);
-      }
-    } else {
+    for (int j = 0; j < kWarpCols / 32; ++j) {
+      if constexpr (kEsize == 4) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        q[i] = pack2<DT>(__uint_as_float(v0[2 * i]) * nrm, __uint_as_float(v0[2 * i + 1]) * nrm);
-        q[16 + i] = pack2<DT>(__uint_as_float(v1[2 * i]) * nrm, __uint_as_float(v1[2 * i + 1]) * nrm);
+        for (int i = 0; i < 32; ++i) q[32 * j + i] = __float_as_uint(__uint_as_float(v[j][i]) * nrm);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          q[16 * j + i] = pack2<DT>(__uint_as_float(v[j][2 * i]) * nrm, __uint_as_float(v[j][2 * i + 1]) * nrm);
       }
     }
     uint8_t *base = (uint8_t *)p.out + (warp >> 2) * kRowBytes;
@@ -275,7 +277,8 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
                  q[4 * i + 3]);
       }
       __syncwarp();
-      constexpr int kPieces = kPassRows * kRowBytes / 16;   // 128 either way
+      constexpr int kPieces = kPassRows * kRowBytes / 16;
+      static_assert(kPieces % 32 == 0, "a pass is a whole number of warp-wide copies");
 #pragma unroll
       for (int k = 0; k < kPieces / 32; ++k) {
         const int c = lane + 32 * k, r = c / (kRowBytes / 16), piece = c % (kRowBytes / 16);
@@ -287,18 +290,18 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
     }
   };
 
-  uint32_t w[2][BW], w_next[2][BW];
-  float nrm[2], nrm_next[2] = {0.f, 0.f};
+  uint32_t w[kLaneRows][BW], w_next[kLaneRows][BW];
+  float nrm[kLaneRows], nrm_next[kLaneRows] = {};
   int64_t tile = blockIdx.x, previous = -1;
   if (tile < tiles) fetch(tile, w, nrm);
   for (int buf = 0; tile < tiles && !gave_up; tile += gridDim.x, buf ^= 1) {
     // the next tile's rows are requested now and used a whole iteration later
     const bool more = tile + gridDim.x < tiles;
     if (more) fetch(tile + gridDim.x, w_next, nrm_next);
-    // ---- decode: warp w rows 16 w .. 16 w + 15, lane (g, t) rows g and g + 8 --------
+    // ---- decode: a warp takes 8 kLaneRows consecutive rows, lane (g, t) row(s) g (+ 8) of them, quarter t
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int row = 16 * warp + 8 * h + g;
+    for (int h = 0; h < kLaneRows; ++h) {
+      const int row = 8 * kLaneRows * warp + 8 * h + g;
       if (t == 0) sts32(kNorms + 512u * buf + 4u * row, __float_as_uint(nrm[h]));
       decode_row<BW>(w[h], sel, M::kAHi, row, t);
       if constexpr (TERMS == 3) decode_row<BW>(w[h], sel | 0x80u, M::kALo, row, t);
@@ -345,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
     previous = gave_up ? -1 : tile;
     if (more) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < kLaneRows; ++h) {
 #pragma unroll
         for (int i = 0; i < BW; ++i) w[h][i] = w_next[h][i];
         nrm[h] = nrm_next[h];
