@@ -33,20 +33,22 @@
 namespace wtq {
 namespace dq5 {
 
-constexpr int kWarps = 16, kThreads = 32 * kWarps;
-constexpr int kLaneRows = 16 / kWarps;             // rows a lane decodes per tile (8 per warp each)
-constexpr int kWarpCols = 128 / (kWarps / 4);      // accumulator columns a warp stores
+// Eight warps decode and feed the tensor cores, eight warps drain the accumulators.
+constexpr int kFeedWarps = 8, kDrainWarps = 8, kWarps = kFeedWarps + kDrainWarps, kThreads = 32 * kWarps;
+constexpr int kLaneRows = 16 / kFeedWarps;         // rows a lane decodes per tile (8 per warp each)
+constexpr int kWarpCols = 128 / (kDrainWarps / 4); // accumulator columns a warp stores
 constexpr uint32_t kBase = 1024;                  // dynamic shared memory is assumed to start at or below this
-constexpr uint32_t kBar = kBase;                  // mbarrier (8 bytes)
-constexpr uint32_t kTmemSlot = kBase + 16;        // tensor-memory address written by tcgen05.alloc
-constexpr uint32_t kNorms = kBase + 64;           // 2 x 128 floats (this tile's and the previous one's)
+constexpr uint32_t kBarDone = kBase;              // 2 mbarriers: the products into accumulator b are complete
+constexpr uint32_t kBarFree = kBase + 16;         // 2 mbarriers: accumulator b has been read out
+constexpr uint32_t kTmemSlot = kBase + 32;        // tensor-memory address written by tcgen05.alloc
+constexpr uint32_t kNorms = kBase + 64;           // 3 x 128 floats: the norms of three tiles in flight
 constexpr uint32_t kCent = kBase + 2048;          // 256 floats: the codebook while the tables are built
 constexpr uint32_t kOperand = 128 * 128 * 2;      // one fp16 operand tile
 constexpr uint32_t kBHi = 4096;
 static_assert(kCent + 1024 <= kBHi, "low region");
 constexpr uint32_t kStage = kBHi + kOperand;      // output staging, per warp (see store_tile)
 constexpr uint32_t kStageBytes = 16 * (2 * kWarpCols + 16);
-static_assert(kStage + kWarps * kStageBytes <= mma::kLutAddr && 8 * (4 * kWarpCols + 16) <= kStageBytes, "staging");
+static_assert(kStage + kDrainWarps * kStageBytes <= mma::kLutAddr && 8 * (4 * kWarpCols + 16) <= kStageBytes, "staging");
 constexpr uint32_t kCols = 256;                   // tensor memory: two accumulators of 128 columns
 constexpr float kOperandScale = 256.f, kResultScale = 1.f / (256.f * 256.f);
 // instruction descriptor: dense, fp32 accumulator, fp16 A and B, both K-major, N = 128, M = 128
@@ -163,7 +165,11 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(kBar) : "memory");
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(kBarDone + 8u * b) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(kBarFree + 8u * b), "r"(kDrainWarps) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   for (int e = tid; e < (1 << BW); e += kThreads)
@@ -210,8 +216,6 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
   const int64_t tiles = (p.N + 127) >> 7;
   const uint32_t L32 = (uint32_t)p.L;
   constexpr int kEsize = DT == WTQ_F32 ? 4 : 2;
-  uint32_t phase = 0;
-  bool gave_up = false;
 
   // packed words and norm of the lane's row(s) of a tile
   const bool dense = p.L == p.MAXLEN;                       // source row = logical row: no plane arithmetic
@@ -238,22 +242,29 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
   };
   // this thread's share of a finished accumulator: lane 32 (warp % 4) + lane, columns
   // kWarpCols (warp / 4) ..
-  auto store_tile = [&](int64_t tile, int buf) {
-    const int lr = 32 * (warp & 3) + lane;
-    const float nrm = __uint_as_float(lds32(kNorms + 512u * buf + 4u * lr));
+  // (a warp may read the tensor-memory lanes 32 (warp % 4) ..; kFeedWarps is a multiple of 4)
+  const int dw = warp - kFeedWarps;                         // index among the draining warps
+  auto store_tile = [&](int64_t tile, int buf, int slot) {
+    const int lr = 32 * (dw & 3) + lane;
+    const float nrm = __uint_as_float(lds32(kNorms + 512u * slot + 4u * lr));
     const uint32_t taddr =
-        tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(128 * buf + kWarpCols * (warp >> 2));
+        tmem + ((uint32_t)(32 * (dw & 3)) << 16) + (uint32_t)(128 * buf + kWarpCols * (dw >> 2));
     uint32_t v[kWarpCols / 32][32];
 #pragma unroll
     for (int i = 0; i < kWarpCols / 32; ++i) tmem_load32(taddr + 32 * i, v[i]);
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+    // the accumulator and the norms are in registers: hand the buffer back
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncwarp();
+    if (lane == 0)
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(kBarFree + 8u * buf) : "memory");
     // The thread holds consecutive columns of ONE row; stored as they are, every
     // store instruction of the warp would touch 32 rows.  A few rows at a time go
     // through a staging area instead and leave as whole row segments.
     constexpr int kRowBytes = kWarpCols * kEsize;           // this warp's part of a row
     constexpr int kPassRows = kEsize == 2 ? 16 : 8;
     constexpr uint32_t kStride = kRowBytes + 16;            // pad: the rows of a pass land in different banks
-    const uint32_t stage = kStage + (uint32_t)warp * kStageBytes;
+    const uint32_t stage = kStage + (uint32_t)dw * kStageBytes;
     uint32_t q[kRowBytes / 4];                              // the row segment, converted
 #pragma unroll
     for (int j = 0; j < kWarpCols / 32; ++j) {
@@ -266,8 +277,8 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
           q[16 * j + i] = pack2<DT>(__uint_as_float(v[j][2 * i]) * nrm, __uint_as_float(v[j][2 * i + 1]) * nrm);
       }
     }
-    uint8_t *base = (uint8_t *)p.out + (warp >> 2) * kRowBytes;
-    const int64_t n0 = (tile << 7) + 32 * (warp & 3);
+    uint8_t *base = (uint8_t *)p.out + (dw >> 2) * kRowBytes;
+    const int64_t n0 = (tile << 7) + 32 * (dw & 3);
 #pragma unroll
     for (int ps = 0; ps < 32 / kPassRows; ++ps) {
       if (lane / kPassRows == ps) {
@@ -290,72 +301,107 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
     }
   };
 
-  uint32_t w[kLaneRows][BW], w_next[kLaneRows][BW];
-  float nrm[kLaneRows], nrm_next[kLaneRows] = {};
-  int64_t tile = blockIdx.x, previous = -1;
-  if (tile < tiles) fetch(tile, w, nrm);
-  for (int buf = 0; tile < tiles && !gave_up; tile += gridDim.x, buf ^= 1) {
-    // the next tile's rows are requested now and used a whole iteration later
-    const bool more = tile + gridDim.x < tiles;
-    if (more) fetch(tile + gridDim.x, w_next, nrm_next);
-    // ---- decode: a warp takes 8 kLaneRows consecutive rows, lane (g, t) row(s) g (+ 8) of them, quarter t
-#pragma unroll
-    for (int h = 0; h < kLaneRows; ++h) {
-      const int row = 8 * kLaneRows * warp + 8 * h + g;
-      if (t == 0) sts32(kNorms + 512u * buf + 4u * row, __float_as_uint(nrm[h]));
-      decode_row<BW>(w[h], sel, M::kAHi, row, t);
-      if constexpr (TERMS == 3) decode_row<BW>(w[h], sel | 0x80u, M::kALo, row, t);
+  // Bounded wait for completion number `use` (0, 1, ...) of an mbarrier; false if it ran out.
+  auto wait_for = [&](uint32_t bar, int use) -> bool {
+    uint32_t done = 0;
+    for (int spin = 0; spin < (1 << 22) && !done; ++spin) {
+      asm volatile(
+          "{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, q;\n\t}\n"
+          : "=r"(done) : "r"(bar), "r"((uint32_t)(use & 1)) : "memory");
     }
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    __syncthreads();
-    // ---- multiply: one thread issues, the barrier hears when the products are done ---
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const uint32_t d = tmem + 128u * buf;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        if constexpr (TERMS == 3) {
-          umma(d, operand_desc(M::kALo, ks), operand_desc(kBHi, ks), ks > 0);
-          umma(d, operand_desc(M::kAHi, ks), operand_desc(M::kBLo, ks), 1u);
-          umma(d, operand_desc(M::kAHi, ks), operand_desc(kBHi, ks), 1u);
-        } else {
-          umma(d, operand_desc(M::kAHi, ks), operand_desc(kBHi, ks), ks > 0);
+    return done != 0;
+  };
+
+  // Tile i of this block uses accumulator i & 1 and norm slot i % 3.  What orders the two
+  // groups of warps:
+  //   done[b]  arrives (tcgen05.commit) when the products of a tile into accumulator b are
+  //            complete: the draining warps may read it, the feeding warps may overwrite the
+  //            operand tile;
+  //   free[b]  arrives (once per draining warp) when accumulator b and its norms are in
+  //            registers: the next products into b may be issued.
+  // Every wait is bounded; whoever runs out of patience marks the state word and leaves its
+  // loop, and the others then run out of patience too.
+  if (warp < kFeedWarps) {
+    uint32_t w[kLaneRows][BW], w_next[kLaneRows][BW];
+    float nrm[kLaneRows], nrm_next[kLaneRows] = {};
+    int64_t tile = blockIdx.x;
+    if (tile < tiles) fetch(tile, w, nrm);
+    for (int i = 0; tile < tiles; tile += gridDim.x, ++i) {
+      const int buf = i & 1, slot = i % 3;
+      // the next tile's rows are requested now and used a whole iteration later
+      const bool more = tile + gridDim.x < tiles;
+      if (more) fetch(tile + gridDim.x, w_next, nrm_next);
+      // the operand tile is free once the previous tile's products are complete
+      uint32_t late = 0;
+      if (i > 0) late = wait_for(kBarDone + 8u * (buf ^ 1), (i - 1) >> 1) ? 0u : 1u;
+      {
+        uint32_t any;                                       // the same answer for all feeding warps
+        asm volatile(
+            "{\n\t.reg .pred q, r;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred r, 1, %2, q;\n\t"
+            "selp.u32 %0, 1, 0, r;\n\t}\n"
+            : "=r"(any) : "r"(late), "r"(32 * kFeedWarps) : "memory");
+        if (any) {
+          if (tid == 0) state[1] = 1;
+          break;
         }
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(kBar)
-                   : "memory");
-    }
-    // ---- store the previous tile while the tensor cores work on this one ---------------
-    if (previous >= 0) store_tile(previous, buf ^ 1);
-    // bounded wait for this tile's products: after it the operand tile may be rewritten
-    {
-      uint32_t done = 0;
-      for (int spin = 0; spin < (1 << 22) && !done; ++spin) {
-        asm volatile(
-            "{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, q;\n\t}\n"
-            : "=r"(done) : "r"(kBar), "r"(phase) : "memory");
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-      if (__syncthreads_or(done == 0)) {              // the same answer for the whole block
-        if (tid == 0) state[1] = 1;
-        gave_up = true;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    }
-    phase ^= 1u;
-    previous = gave_up ? -1 : tile;
-    if (more) {
+      // ---- decode: a warp takes 16 consecutive rows, lane (g, t) rows g and g + 8 of them, quarter t
 #pragma unroll
       for (int h = 0; h < kLaneRows; ++h) {
+        const int row = 8 * kLaneRows * warp + 8 * h + g;
+        if (t == 0) sts32(kNorms + 512u * slot + 4u * row, __float_as_uint(nrm[h]));
+        decode_row<BW>(w[h], sel, M::kAHi, row, t);
+        if constexpr (TERMS == 3) decode_row<BW>(w[h], sel | 0x80u, M::kALo, row, t);
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      asm volatile("bar.sync 1, %0;\n" ::"r"(32 * kFeedWarps) : "memory");
+      // ---- multiply: one thread issues into accumulator buf once it has been read out ------
+      if (tid == 0) {
+        bool ok = true;
+        if (i >= 2) ok = wait_for(kBarFree + 8u * buf, (i - 2) >> 1);
+        if (ok) {
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t d = tmem + 128u * buf;
 #pragma unroll
-        for (int i = 0; i < BW; ++i) w[h][i] = w_next[h][i];
-        nrm[h] = nrm_next[h];
+          for (int ks = 0; ks < 8; ++ks) {
+            if constexpr (TERMS == 3) {
+              umma(d, operand_desc(M::kALo, ks), operand_desc(kBHi, ks), ks > 0);
+              umma(d, operand_desc(M::kAHi, ks), operand_desc(M::kBLo, ks), 1u);
+              umma(d, operand_desc(M::kAHi, ks), operand_desc(kBHi, ks), 1u);
+            } else {
+              umma(d, operand_desc(M::kAHi, ks), operand_desc(kBHi, ks), ks > 0);
+            }
+          }
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+                       ::"r"(kBarDone + 8u * buf) : "memory");
+        } else {
+          state[1] = 1;        // nothing is issued: every later wait on done[] runs out as well
+        }
+      }
+      if (more) {
+#pragma unroll
+        for (int h = 0; h < kLaneRows; ++h) {
+#pragma unroll
+          for (int k = 0; k < BW; ++k) w[h][k] = w_next[h][k];
+          nrm[h] = nrm_next[h];
+        }
       }
     }
+  } else {
+    int64_t tile = blockIdx.x;
+    for (int i = 0; tile < tiles; tile += gridDim.x, ++i) {
+      const int buf = i & 1;
+      const bool ok = wait_for(kBarDone + 8u * buf, i >> 1);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) state[1] = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      store_tile(tile, buf, i % 3);
+    }
   }
-  if (previous >= 0) store_tile(previous, (int)(((previous - blockIdx.x) / gridDim.x) & 1));
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 0)
