@@ -59,7 +59,10 @@ template <int BW, int TERMS> struct Map {
   static constexpr uint32_t kAHi = mma::kLutAddr + kLutBytes;
   static constexpr uint32_t kALo = kAHi + kOperand;
   static constexpr uint32_t kBLo = kALo + kOperand;
-  static constexpr uint32_t kDynamic = TERMS == 3 ? kBLo + kOperand : kAHi + kOperand;
+  // the single-term form has room for two operand tiles: tile i + 1 is decoded while the
+  // tensor cores still read tile i
+  static constexpr int kOperandTiles = TERMS == 3 ? 1 : 2;
+  static constexpr uint32_t kDynamic = TERMS == 3 ? kBLo + kOperand : kAHi + 2 * kOperand;
   static_assert(kDynamic <= 227u * 1024u, "shared memory budget");
 };
 
@@ -332,9 +335,15 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
       // the next tile's rows are requested now and used a whole iteration later
       const bool more = tile + gridDim.x < tiles;
       if (more) fetch(tile + gridDim.x, w_next, nrm_next);
-      // the operand tile is free once the previous tile's products are complete
+      // the operand tile this one is decoded into is free once the products of the tile that
+      // used it last (the previous tile, or the one before with two operand tiles) are complete
       uint32_t late = 0;
-      if (i > 0) late = wait_for(kBarDone + 8u * (buf ^ 1), (i - 1) >> 1) ? 0u : 1u;
+      const uint32_t a_hi = M::kAHi + (M::kOperandTiles == 2 ? (uint32_t)buf * kOperand : 0u);
+      if constexpr (M::kOperandTiles == 2) {
+        if (i > 1) late = wait_for(kBarDone + 8u * buf, (i - 2) >> 1) ? 0u : 1u;
+      } else {
+        if (i > 0) late = wait_for(kBarDone + 8u * (buf ^ 1), (i - 1) >> 1) ? 0u : 1u;
+      }
       {
         uint32_t any;                                       // the same answer for all feeding warps
         asm volatile(
@@ -351,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
       for (int h = 0; h < kLaneRows; ++h) {
         const int row = 8 * kLaneRows * warp + 8 * h + g;
         if (t == 0) sts32(kNorms + 512u * slot + 4u * row, __float_as_uint(nrm[h]));
-        decode_row<BW>(w[h], sel, M::kAHi, row, t);
+        decode_row<BW>(w[h], sel, a_hi, row, t);
         if constexpr (TERMS == 3) decode_row<BW>(w[h], sel | 0x80u, M::kALo, row, t);
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -371,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1) dequant_umma_kernel(DequantParams
               umma(d, operand_desc(M::kAHi, ks), operand_desc(M::kBLo, ks), 1u);
               umma(d, operand_desc(M::kAHi, ks), operand_desc(kBHi, ks), 1u);
             } else {
-              umma(d, operand_desc(M::kAHi, ks), operand_desc(kBHi, ks), ks > 0);
+              umma(d, operand_desc(a_hi, ks), operand_desc(kBHi, ks), ks > 0);
             }
           }
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
