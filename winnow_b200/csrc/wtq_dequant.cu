@@ -4,7 +4,8 @@
 // (planes, MAXLEN, NB) buffer viewed through its first L positions
 // (turboquant_kv/kernel.py:47-53).
 //
-// Two kernels:
+// Two kernels here, and the tcgen05 kernel of wtq_dequant_umma.cu, which the
+// tensor-core modes try first:
 //
 // dequant_kernel (any D <= 256, any width): fp32 on the CUDA cores.  A block
 // takes kRows rows; their centroid values sit in shared memory; thread c owns
