@@ -89,3 +89,27 @@ def test_auto_splits_fills_the_last_round_of_worker_warps():
     assert 1 <= f(1, 8, 1, 128, 1 << 20, 16, 4, 4) <= 1024
     # shapes without a tensor-core kernel use the generic rule and stay in range
     assert 1 <= f(4, 8, 2, 64, 64, 16, 8, 8) <= 1024
+
+
+def test_prefill_planning_is_host_only(library):
+    """Chunk counts and workspace sizes of the chunked-prefill entry point are
+    plain host arithmetic (148 multiprocessors assumed when no GPU is present)."""
+    L = _lib.lib()
+    # 16 x 8 kv heads x 256 query rows: 128 groups, two history chunks fill 148 SMs
+    assert L.wtq_prefill_auto_splits(16, 32, 8, 64, 512, 16) == 2
+    # one sequence: 8 groups, many chunks of at least 256 tokens
+    assert L.wtq_prefill_auto_splits(1, 32, 8, 64, 8192, 16) == 28
+    # a history shorter than one chunk is never split
+    assert L.wtq_prefill_auto_splits(2, 8, 2, 7, 6, 16) == 1
+    rows = 16 * 64 * 32
+    expect = (256 + 4096 + rows * 128 * 4 + rows * 2 * 128 * 4 + 2 * rows * 2 * 4 + 256 * 256)
+    assert L.wtq_prefill_workspace_bytes(16, 32, 8, 64, 128, 2) == expect
+    assert L.wtq_prefill_workspace_bytes(0, 32, 8, 64, 128, 2) == 0
+
+
+def test_dequant_mode_argument_errors(library):
+    L = _lib.lib()
+    assert L.wtq_dequant_mode(None, None, None, None, None, 2, 4, 128, 5, 5, 5, 9, None) == -1
+    assert b"bad mode" in L.wtq_last_error()
+    assert L.wtq_dequant_mode(None, None, None, None, None, 2, 4, 128, 0, 1, 1, _lib.DEQUANT_TC, None) == 0
+    assert L.wtq_dequant_mode(None, None, None, None, None, 2, 7, 128, 4, 4, 4, _lib.DEQUANT_AUTO, None) == -1
