@@ -597,13 +597,23 @@ extern "C" int wtq_prefill_auto_splits(int B, int Hq, int Hkv, int Q, int max_pa
   const int64_t max_tokens = (int64_t)max_pages * S;
   const int row_blocks = (Q * (Hq / Hkv) + pf::kRows - 1) / pf::kRows;
   const int64_t groups = (int64_t)B * Hkv * row_blocks;
-  // Enough items to keep every multiprocessor busy and no more: each further
-  // chunk adds a set of chunk states to write and merge (measured at 16 x 8 kv
-  // heads x 8k tokens, 64 query tokens: 2 chunks 866 us, 5 chunks 940 us, 16
-  // chunks 1097 us per call).  Chunks of at least 256 tokens.
-  int64_t splits = (3 * (int64_t)device_sms() / 2 + groups - 1) / groups;
-  const int64_t most = std::max<int64_t>(1, max_tokens / 256);
-  splits = std::max<int64_t>(1, std::min<int64_t>(splits, std::min<int64_t>(most, 256)));
+  // Items = groups x chunks run in waves of one per multiprocessor; every chunk beyond the
+  // first adds about 5 % (states to write and merge, queries to reload).  Both effects were
+  // measured at 16 x 8 kv heads x 8k tokens: 64 query tokens (128 groups) 690 / 726 / 769 us
+  // with 1 / 2 / 3 chunks, 256 query tokens (512 groups) 2549 / 2388 / 2633 us.  Take the
+  // count with the lowest modelled cost; chunks of at least 256 tokens.
+  const int64_t sms = device_sms();
+  const int64_t most = std::max<int64_t>(1, std::min<int64_t>(max_tokens / 256, 32));
+  int64_t splits = 1;
+  double best = 0.0;
+  for (int64_t s = 1; s <= most; ++s) {
+    const int64_t items = groups * s, waves = (items + sms - 1) / sms;
+    const double cost = (1.0 + 0.05 * (double)(s - 1)) * (double)(waves * sms) / (double)items;
+    if (s == 1 || cost < best - 1e-9) {
+      best = cost;
+      splits = s;
+    }
+  }
   // chunk sizes round up to whole tiles: drop chunks that would stay empty
   const int tokens = pf::chunk_tokens_for((int)max_tokens, (int)splits);
   return (int)((max_tokens + tokens - 1) / tokens);
