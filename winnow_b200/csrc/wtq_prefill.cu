@@ -21,11 +21,11 @@
 //            them as a [token][coordinate] tile, 16-byte pieces XOR-swizzled by
 //            the row so that ldmatrix reads it without bank conflicts;
 //   scores   each warp owns 32 query rows: S = Q K^T with mma.m16n8k16 (A: query
-//            fragments by ldmatrix, B: key tile by ldmatrix), times the key
-//            norms, causal mask where the tile reaches a row's limit;
+//            fragments by ldmatrix, B: key tile by ldmatrix; the tile holds
+//            centroid x norm), causal mask where the tile reaches a row's limit;
 //   softmax  online, in the exp2 domain, on the score fragments in registers;
-//   values   O += (P * value norms) V, the probability fragments feeding the MMA
-//            as A operands directly, V by ldmatrix.trans.
+//   values   O += P V (V tile = centroid x norm), the probability fragments
+//            feeding the MMA as A operands directly, V by ldmatrix.trans.
 //
 // fp16 scores are exact enough while they are small; a warp whose tile holds a
 // score beyond 8 (log2 domain) recomputes that tile's scores in fp32 from the
@@ -132,19 +132,35 @@ __device__ __forceinline__ void decode_piece(const uint32_t (&w)[BW], uint32_t s
 
 // One warp decodes tokens 16 u .. 16 u + 15 of one side: the lane (g, t) takes
 // rows g and g + 8 and coordinates 32 t .. 32 t + 31 of each.
+// The values stored are centroid x row norm, rounded to fp16 (`norms` = address of the
+// tile's fp16 norms; rows from `valid` on get norm 0): the scores and the value sums then
+// need no per-token scaling.
 template <int BW>
-__device__ __forceinline__ void decode_group(uint32_t raw, uint32_t tile, uint32_t sel, int u, int g, int t) {
+__device__ __forceinline__ void decode_group(uint32_t raw, uint32_t norms, int valid, uint32_t tile,
+                                             uint32_t sel, int u, int g, int t) {
   constexpr int NB = 16 * BW;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = 16 * u + g + 8 * h;
     uint32_t w[BW];
     load_words<4 * BW>(raw + (uint32_t)row * NB + (uint32_t)t * (4 * BW), w);
+    unsigned short nh;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(nh) : "r"(norms + 2u * row));
+    if (row >= valid) nh = 0;
+    const __half2 n2 = __half2half2(__ushort_as_half(nh));
+    auto scaled = [&](uint32_t x) {
+      const __half2 y = __hmul2(*reinterpret_cast<const __half2 *>(&x), n2);
+      return *reinterpret_cast<const uint32_t *>(&y);
+    };
     uint32_t f[4];
-    decode_piece<BW, 0>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 0), f[0], f[1], f[2], f[3]);
-    decode_piece<BW, 1>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 1), f[0], f[1], f[2], f[3]);
-    decode_piece<BW, 2>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 2), f[0], f[1], f[2], f[3]);
-    decode_piece<BW, 3>(w, sel, f); sts128(tile_at(tile, row, 4 * t + 3), f[0], f[1], f[2], f[3]);
+    decode_piece<BW, 0>(w, sel, f);
+    sts128(tile_at(tile, row, 4 * t + 0), scaled(f[0]), scaled(f[1]), scaled(f[2]), scaled(f[3]));
+    decode_piece<BW, 1>(w, sel, f);
+    sts128(tile_at(tile, row, 4 * t + 1), scaled(f[0]), scaled(f[1]), scaled(f[2]), scaled(f[3]));
+    decode_piece<BW, 2>(w, sel, f);
+    sts128(tile_at(tile, row, 4 * t + 2), scaled(f[0]), scaled(f[1]), scaled(f[2]), scaled(f[3]));
+    decode_piece<BW, 3>(w, sel, f);
+    sts128(tile_at(tile, row, 4 * t + 3), scaled(f[0]), scaled(f[1]), scaled(f[2]), scaled(f[3]));
   }
 }
 
@@ -352,19 +368,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
       // (norms are copied eight tokens at a time: those of tokens past the end of
       // the tile's range are whatever the page holds and become 0 here)
       if (warp < 4) {
-        decode_group<BWK>(raw, kKTile, sel_k, warp, g, t);
-        if (lane < 16) {
+        decode_group<BWK>(raw, raw + M::kRawNK, end - tok0, kKTile, sel_k, warp, g, t);
+        if (lane < 16) {                                     // fp32 norms, for the fp32 re-scoring only
           const int tk = 16 * warp + lane;
           const float v = tok0 + tk < end ? lds_half(raw + M::kRawNK + 2u * tk) : 0.f;
           sts32(kNormK + 4u * tk, __float_as_uint(v));
         }
       } else {
-        decode_group<BWV>(raw + M::kRawV, kVTile, sel_v, warp - 4, g, t);
-        if (lane < 16) {
-          const int tk = 16 * (warp - 4) + lane;
-          const float v = tok0 + tk < end ? lds_half(raw + M::kRawNV + 2u * tk) : 0.f;
-          sts32(kNormV + 4u * tk, __float_as_uint(v));
-        }
+        decode_group<BWV>(raw + M::kRawV, raw + M::kRawNV, end - tok0, kVTile, sel_v, warp - 4, g, t);
       }
       __syncthreads();
       if (j + 1 < ntiles) copy(j + 1);
@@ -395,19 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
           }
         }
       }
-      float nk[8][2];
-#pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const float2 v = lds_f2(kNormK + 4u * (8 * n + 2 * t));
-        nk[n][0] = v.x; nk[n][1] = v.y;
-      }
       const bool masked = tok0 + kTile > warp_lo;            // some row of the warp stops inside the tile
-#pragma unroll
-      for (int m = 0; m < 2; ++m)
-#pragma unroll
-        for (int n = 0; n < 8; ++n)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) s[m][n][e] *= nk[n][e & 1];
       if (masked) {
 #pragma unroll
         for (int m = 0; m < 2; ++m)
@@ -453,13 +452,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
             const int tk = 8 * n + 2 * t + c;
             const float4 r = precise_token<BWK>(raw + (uint32_t)tk * M::kNBK, qp[0], qp[1], qp[2], qp[3],
                                                 p.k.centroids);
+            const float nk_tk = __uint_as_float(lds32(kNormK + 4u * tk));
             const float x[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
             for (int m = 0; m < 2; ++m)
 #pragma unroll
               for (int h = 0; h < 2; ++h)
                 s[m][n][2 * h + c] = masked && tok0 + tk >= limit[m][h] ? -INFINITY
-                                                                        : x[2 * m + h] * nk[n][c];
+                                                                        : x[2 * m + h] * nk_tk;
           }
         row_maxima();
       }
@@ -488,12 +488,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
           }
         }
       }
-      float nv[8][2];
-#pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const float2 v = lds_f2(kNormV + 4u * (8 * n + 2 * t));
-        nv[n][0] = v.x; nv[n][1] = v.y;
-      }
       uint32_t pa[2][8][2];                                  // P * value norm as fp16 pairs
       float base[2][2];
 #pragma unroll
@@ -507,8 +501,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
           const float p2 = ex2(s[m][n][2] - base[m][1]), p3 = ex2(s[m][n][3] - base[m][1]);
           sum[m][0] += p0 + p1;
           sum[m][1] += p2 + p3;
-          pa[m][n][0] = pack_half2(p0 * nv[n][0], p1 * nv[n][1]);    // every norm in the tile is finite
-          pa[m][n][1] = pack_half2(p2 * nv[n][0], p3 * nv[n][1]);
+          pa[m][n][0] = pack_half2(p0, p1);
+          pa[m][n][1] = pack_half2(p2, p3);
         }
       };
 
