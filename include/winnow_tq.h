@@ -236,11 +236,19 @@ int wtq_dense_decode(const void *q, int q_dtype, const int64_t q_strides[2], voi
  * Requires what the tensor-core decode path requires (head_dim 128, widths
  * 4/4, 4/6, 6/6, 8/8, power-of-two page size >= 16, Hq / Hkv <= 8, 16-byte
  * aligned pages); otherwise WTQ_ERR_UNSUPPORTED, and the caller may run the
- * B * Q rows through wtq_decode instead.  num_splits <= 0 picks the number of
- * history chunks (wtq_prefill_auto_splits); the workspace must hold
- * wtq_prefill_workspace_bytes(..., num_splits) for the value used.  Status bits
- * as for wtq_decode.  Four launches, no allocation, no synchronisation. */
+ * B * Q rows through wtq_decode instead.  num_splits > 0 cuts every history
+ * into that many equal chunks.  num_splits <= 0 leaves the schedule to the
+ * library: with enough groups and rows the 64-token tiles of all histories are
+ * dealt evenly to the thread blocks (at most three chunk states per row),
+ * otherwise equal chunks from a cost model; wtq_prefill_auto_splits returns the
+ * number of chunk states per row that choice needs, and the workspace must hold
+ * wtq_prefill_workspace_bytes(..., num_splits) for that number (or for the
+ * explicit num_splits).  Status bits as for wtq_decode.  Three launches and up
+ * to two small memsets, no allocation, no synchronisation. */
 int wtq_prefill_auto_splits(int B, int Hq, int Hkv, int Q, int max_pages, int S);
+/* Schedule of this thread's last wtq_prefill call that got as far as launching:
+ * 0 equal chunks, 1 tiles dealt evenly to the blocks; -1 before any call. */
+int wtq_prefill_last_schedule(void);
 size_t wtq_prefill_workspace_bytes(int B, int Hq, int Hkv, int Q, int D, int num_splits);
 int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2], void *out,
                 const int64_t out_strides[2], const wtq_side_t *k_side, const wtq_side_t *v_side,

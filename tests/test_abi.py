@@ -95,10 +95,13 @@ def test_prefill_planning_is_host_only(library):
     """Chunk counts and workspace sizes of the chunked-prefill entry point are
     plain host arithmetic (148 multiprocessors assumed when no GPU is present)."""
     L = _lib.lib()
-    # 16 x 8 kv heads x 256 query rows: 128 groups fit one wave, a second chunk only costs
-    assert L.wtq_prefill_auto_splits(16, 32, 8, 64, 512, 16) == 1
-    # four times the query rows: 512 groups are 3.46 waves, 1024 items 6.92
-    assert L.wtq_prefill_auto_splits(16, 32, 8, 256, 512, 16) == 2
+    # 16 x 8 kv heads x 256 query rows: 128 groups and 32768 rows take the balanced
+    # schedule (tiles dealt evenly to the blocks), three chunk states per row
+    assert L.wtq_prefill_auto_splits(16, 32, 8, 64, 512, 16) == 3
+    assert L.wtq_prefill_auto_splits(16, 32, 8, 256, 512, 16) == 3
+    # 32 groups are too few for it: equal chunks from the cost model, 128 items in one wave
+    assert L.wtq_prefill_auto_splits(4, 32, 8, 64, 512, 16) == 4
+    assert L.wtq_prefill_auto_splits(1, 32, 8, 256, 8192, 16) == 4
     # one sequence: 8 groups, chunks until a wave is nearly full (144 items)
     assert L.wtq_prefill_auto_splits(1, 32, 8, 64, 8192, 16) == 18
     # a history shorter than one chunk is never split

@@ -7,7 +7,7 @@ The cases cover chunk lengths 2, 16, 64 and 256, chunks longer than a
 sequence's whole history (its first tokens see nothing and return zeros),
 empty sequences, every width pair that has a tensor-core kernel, page sizes 16
 to 64, 1 to 8 query heads per kv head, explicit and automatic chunking of the
-history, query scales that push the scores beyond what fp16 score arithmetic
+history, the balanced schedule, query scales that push the scores beyond what fp16 score arithmetic
 is trusted with, and the fallback for layouts the kernel does not serve.
 """
 import pytest
@@ -117,6 +117,34 @@ def test_many_rows_rotate_and_merge_on_the_tensor_cores(dtype, splits):
         _check(q, okv, splits=splits)
     else:
         _check(q, okv, splits=splits, dtype=dtype, atol=2e-2, rel_l2=1e-2)
+
+
+@pytest.mark.parametrize("lens,widths,dtype", [
+    ((900, 0, 65, 300, 2000), (4, 4), torch.float32),        # ragged: runs of half the longest group
+    ((1000,) * 10, (4, 4), torch.float32),                   # even: runs of a 148th of all tiles
+    ((40, 1500, 64, 129, 700, 3), (6, 6), torch.bfloat16),   # chunks longer than some histories
+    ((2100, 1, 640, 333, 70), (8, 8), torch.float16),
+])
+def test_balanced_schedule(lens, widths, dtype):
+    """At least 74 groups and 4096 query rows: left to the library, the 64-token
+    tiles of all histories are dealt evenly to the blocks, a group's pieces land
+    in up to three chunk slots and rows that see nothing of a piece leave their
+    slot empty.  Same answers as the oracle."""
+    B, Hq, Hkv, Q = len(lens), 32, 8, 70
+    q, okv = _case(740 + len(lens) + widths[0], B, Hq, Hkv, lens, 16, widths[0], widths[1], Q)
+    max_pages = okv.page_table.shape[1]
+    assert _lib.lib().wtq_prefill_auto_splits(B, Hq, Hkv, Q, max_pages, 16) == 3
+    if dtype == torch.float32:
+        out, ref = _check(q, okv)
+    else:
+        out, ref = _check(q, okv, dtype=dtype, atol=2e-2, rel_l2=1e-2)
+    assert _lib.lib().wtq_prefill_last_schedule() == 1          # the balanced schedule did run
+    for b, L in enumerate(lens):
+        if L < Q:
+            assert (out[b, :, :Q - L] == 0).all()                # tokens before the sequence's history
+    _check(q, okv, splits=2, dtype=dtype, atol=2e-2 if dtype != torch.float32 else 2e-3,
+           rel_l2=1e-2 if dtype != torch.float32 else 1e-3)
+    assert _lib.lib().wtq_prefill_last_schedule() == 0          # an explicit count means equal chunks
 
 
 def test_tiled_compressed_attention_uses_the_chunk_kernel():

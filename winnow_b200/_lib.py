@@ -87,6 +87,7 @@ _SIGNATURES = {
                                  c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
     "wtq_prefill_auto_splits": (c_int, [c_int] * 6),
+    "wtq_prefill_last_schedule": (c_int, []),
     "wtq_prefill_workspace_bytes": (c_size_t, [c_int] * 6),
     "wtq_prefill": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int64), c_void_p, ctypes.POINTER(c_int64),
                             ctypes.POINTER(Side), ctypes.POINTER(Side), c_void_p, c_int64, c_void_p,

@@ -50,8 +50,12 @@ constexpr uint32_t kKTile = kBase;              // [64][128] fp16
 constexpr uint32_t kVTile = kKTile + kTile * 256;
 constexpr uint32_t kNormK = kVTile + kTile * 256;   // 64 floats each
 constexpr uint32_t kNormV = kNormK + kTile * 4;
-constexpr uint32_t kItem = kNormV + kTile * 4;      // the item being worked on
-static_assert(kItem + 16 <= mma::kLutAddr, "tiles must end below the lookup tables");
+constexpr uint32_t kItem = kNormV + kTile * 4;      // the item being worked on (8 words)
+constexpr uint32_t kWalk = kItem + 32;              // balanced schedule: where this block stands (10 words)
+constexpr uint32_t kPlan = kWalk + 64;              // balanced schedule: tiles of every (sequence, row block)
+constexpr int kMaxPairs = 4096;                     // (sequence, row block) pairs the plan has room for
+constexpr int kBalancedSlots = 3;                   // a group is cut by at most two block boundaries
+static_assert(kPlan + 4 * kMaxPairs <= mma::kLutAddr, "tiles and the plan must end below the lookup tables");
 constexpr float kPreciseAbove = 8.f;            // |score| (log2 domain) beyond which fp16 is not trusted
 
 struct Params {
@@ -63,6 +67,7 @@ struct Params {
   int32_t *row_lens;         // (B * Q) causal lengths, written here for the merge
   int B, Hq, Hkv, n_rep, Q, S, P, max_pages, max_tokens;
   int num_splits, chunk_tokens, row_blocks;
+  int balanced;              // 1: tiles dealt evenly to the blocks (chunk_tokens unused), 0: equal chunks
   float *part_acc, *part_m, *part_l;
   int32_t *status, *work_counter;
   const uint32_t *lut;
@@ -221,17 +226,115 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
   const int items = p.B * p.Hkv * p.row_blocks * p.num_splits;
   const int page_shift = 31 - __clz(p.S);
 
+  // ---- balanced schedule ---------------------------------------------------------------
+  // The 64-token tiles of all groups, laid end to end (sequence, row block, kv head), are
+  // cut into one equal run per block, so every multiprocessor gets the same number of
+  // tiles whatever the number of groups.  A run is at least half the longest group, hence a
+  // group is cut at most twice and its pieces take chunk slots 0..2; the slot of a piece is
+  // its block's distance from the block that holds the group's first tile.
+  if (p.balanced) {
+    const int pairs = p.B * p.row_blocks;
+    for (int i = tid; i < pairs; i += kThreads) {
+      const int b = i / p.row_blocks, rb = i - b * p.row_blocks;
+      int L = p.seq_lens[b];
+      L = L < 0 ? 0 : (L > p.max_tokens ? p.max_tokens : L);
+      const int last = min(R, (rb + 1) * kRows) - 1;          // last row of the block
+      const int len = L - p.Q + 1 + last / p.n_rep;
+      sts32(kPlan + 4u * i, len > 0 ? (uint32_t)((len + kTile - 1) / kTile) : 0u);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      long long total = 0;
+      int longest = 0;
+      for (int i = lane; i < pairs; i += 32) {
+        const int n = (int)lds32(kPlan + 4u * i);
+        total += n;
+        longest = max(longest, n);
+      }
+#pragma unroll
+      for (int d = 16; d; d >>= 1) {
+        total += __shfl_xor_sync(kFull, total, d);
+        longest = max(longest, __shfl_xor_sync(kFull, longest, d));
+      }
+      if (lane == 0) {
+        total *= p.Hkv;
+        long long share = (total + gridDim.x - 1) / gridDim.x;
+        share = max(share, (long long)((longest + 1) / 2));
+        share = max(share, 1LL);
+        const long long lo = min(total, share * blockIdx.x), hi = min(total, lo + share);
+        sts32(kWalk + 0, 0u);                                             // pair the walk stands in
+        sts32(kWalk + 4, 0u); sts32(kWalk + 8, 0u);                       // tiles before that pair
+        sts32(kWalk + 12, (uint32_t)lo); sts32(kWalk + 16, (uint32_t)(lo >> 32));   // next tile
+        sts32(kWalk + 20, (uint32_t)hi); sts32(kWalk + 24, (uint32_t)(hi >> 32));   // end of the run
+        sts32(kWalk + 28, (uint32_t)share); sts32(kWalk + 32, (uint32_t)(share >> 32));
+      }
+    }
+  }
+  auto walk64 = [&](uint32_t at) -> long long {
+    return (long long)(((unsigned long long)lds32(at + 4) << 32) | lds32(at));
+  };
+
   for (;;) {
     __syncthreads();                                        // everyone is done with the previous item
-    if (tid == 0) sts32(kItem, (uint32_t)atomicAdd(p.work_counter, 1));
+    if (tid == 0) {
+      if (!p.balanced) {
+        sts32(kItem, (uint32_t)atomicAdd(p.work_counter, 1));
+      } else {
+        int i = (int)lds32(kWalk);
+        long long pre = walk64(kWalk + 4), x = walk64(kWalk + 12);
+        const long long hi = walk64(kWalk + 20), share = walk64(kWalk + 28);
+        if (x >= hi) {
+          sts32(kItem, 0xffffffffu);
+        } else {
+          int n = (int)lds32(kPlan + 4u * i);
+          // ends before the last pair: x < hi <= all tiles (the bound on i only guards the plan)
+          while (x >= pre + (long long)p.Hkv * n && i + 1 < p.B * p.row_blocks) {
+            pre += (long long)p.Hkv * n;
+            n = (int)lds32(kPlan + 4u * ++i);
+          }
+          const long long rel = x - pre;
+          const int kvh = n > 0 ? (int)(rel / n) : p.Hkv, off = (int)(rel - (long long)kvh * n);
+          const int take = (int)min(hi - x, (long long)(n - off));
+          const long long slot = (long long)blockIdx.x - (pre + (long long)kvh * n) / share;
+          if (slot < 0 || slot >= p.num_splits || kvh >= p.Hkv || take < 1) {   // cannot happen; never
+            x = hi - take;                                                      // write outside the states
+            if (p.status) atomicOr(p.status, WTQ_STATUS_LAYOUT);
+            sts32(kItem, 0xffffffffu);
+          } else {
+            sts32(kItem, (uint32_t)i);
+            sts32(kItem + 4, (uint32_t)kvh);
+            sts32(kItem + 8, (uint32_t)off);
+            sts32(kItem + 12, (uint32_t)(off + take));
+            sts32(kItem + 16, (uint32_t)slot);
+          }
+          x += take;
+          sts32(kWalk, (uint32_t)i);
+          sts32(kWalk + 4, (uint32_t)pre); sts32(kWalk + 8, (uint32_t)(pre >> 32));
+          sts32(kWalk + 12, (uint32_t)x); sts32(kWalk + 16, (uint32_t)(x >> 32));
+        }
+      }
+    }
     __syncthreads();
     const int item = (int)lds32(kItem);
-    if (item >= items) break;
-    // chunks vary fastest, so blocks working at the same time share the query rows in L2
-    const int chunk = item % p.num_splits;
-    const int rb = (item / p.num_splits) % p.row_blocks;
-    const int kvh = (item / (p.num_splits * p.row_blocks)) % p.Hkv;
-    const int b = item / (p.num_splits * p.row_blocks * p.Hkv);
+    int chunk, rb, kvh, b, start, cap;                       // cap: end of the item's token range
+    if (!p.balanced) {
+      if (item >= items) break;
+      // chunks vary fastest, so blocks working at the same time share the query rows in L2
+      chunk = item % p.num_splits;
+      rb = (item / p.num_splits) % p.row_blocks;
+      kvh = (item / (p.num_splits * p.row_blocks)) % p.Hkv;
+      b = item / (p.num_splits * p.row_blocks * p.Hkv);
+      start = chunk * p.chunk_tokens;
+      cap = start + p.chunk_tokens;
+    } else {
+      if (item < 0) break;
+      b = item / p.row_blocks;
+      rb = item - b * p.row_blocks;
+      kvh = (int)lds32(kItem + 4);
+      start = (int)lds32(kItem + 8) * kTile;
+      cap = (int)lds32(kItem + 12) * kTile;
+      chunk = (int)lds32(kItem + 16);
+    }
     int L = p.seq_lens[b];
     L = L < 0 ? 0 : (L > p.max_tokens ? p.max_tokens : L);
     const int row_lo = rb * kRows;
@@ -240,10 +343,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
       const int len = L - p.Q + 1 + row / p.n_rep;
       return len < 0 ? 0 : len;
     };
-    const int start = chunk * p.chunk_tokens;
     const int len_last = length_of(row_hi - 1);
     if (row_lo >= R || start >= len_last) continue;         // no row of the block sees this chunk
-    const int end = min(start + p.chunk_tokens, len_last);
+    const int end = min(cap, len_last);
     const int ntiles = (end - start + kTile - 1) / kTile;
 
     // ---- this lane's four rows ------------------------------------------------
@@ -254,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int row = wrow0 + 16 * m + 8 * h + g;
-        limit[m][h] = min(row < row_hi ? length_of(row) : 0, start + p.chunk_tokens);
+        limit[m][h] = min(row < row_hi ? length_of(row) : 0, cap);
       }
     // index of a row's rotated query (and, times num_splits, of its chunk states); -1: no such row
     auto query_row = [&](int m, int h) -> int64_t {
@@ -264,22 +366,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
       return ((int64_t)b * p.Q + i) * p.Hq + kvh * p.n_rep + r;
     };
     // rows are in causal order: the warp's first and last existing rows bound its limits
-    const int warp_hi = wrow0 < row_hi ? min(length_of(min(wrow0 + 31, row_hi - 1)), start + p.chunk_tokens) : 0;
-    const int warp_lo = wrow0 < row_hi ? min(length_of(wrow0), start + p.chunk_tokens) : 0;
+    const int warp_hi = wrow0 < row_hi ? min(length_of(min(wrow0 + 31, row_hi - 1)), cap) : 0;
+    const int warp_lo = wrow0 < row_hi ? min(length_of(wrow0), cap) : 0;
     const bool warp_on = warp_hi > start;
-
-    // ---- query rows -> fp16 tile -------------------------------------------------
-    for (int e = tid; e < kRows * 32; e += kThreads) {      // 32 float4 per row
-      const int lr = e >> 5, c4 = e & 31, row = row_lo + lr;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row < row_hi) {
-        const int i = row / p.n_rep, r = row - i * p.n_rep;
-        const int64_t qrow = ((int64_t)b * p.Q + i) * p.Hq + kvh * p.n_rep + r;
-        v = __ldg(reinterpret_cast<const float4 *>(p.q_rot + qrow * 128) + c4);
-      }
-      sts64u(tile_at(M::kQTile, lr, c4 >> 1) + (uint32_t)(c4 & 1) * 8u, pack_half2(v.x, v.y),
-             pack_half2(v.z, v.w));
-    }
 
     // ---- copy of one tile into a landing buffer ----------------------------------
     // Done in two steps so that the page-table reads are not in front of the
@@ -346,6 +435,27 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(Params p) {
     lookup(0);
     copy(0);
     if (ntiles > 1) lookup(1);
+
+    // ---- query rows -> fp16 tile (behind the first copy, eight loads in flight per thread) ----
+    for (int e0 = tid; e0 < kRows * 32; e0 += 8 * kThreads) {  // 32 float4 per row
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int e = e0 + u * kThreads, lr = e >> 5, c4 = e & 31, row = row_lo + lr;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < row_hi) {
+          const int i = row / p.n_rep, r = row - i * p.n_rep;
+          const int64_t qrow = ((int64_t)b * p.Q + i) * p.Hq + kvh * p.n_rep + r;
+          v[u] = __ldg(reinterpret_cast<const float4 *>(p.q_rot + qrow * 128) + c4);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int e = e0 + u * kThreads, lr = e >> 5, c4 = e & 31;
+        sts64u(tile_at(M::kQTile, lr, c4 >> 1) + (uint32_t)(c4 & 1) * 8u, pack_half2(v[u].x, v[u].y),
+               pack_half2(v[u].z, v[u].w));
+      }
+    }
 
     float o[2][16][4];                                      // rows x coordinates of the value basis
     float mx[2][2], sum[2][2];
@@ -566,7 +676,7 @@ int launch(const Params &p, cudaStream_t stream) {
     opted_in_dev[dev & 63].store(true, std::memory_order_release);
   }
   const int64_t items = (int64_t)p.B * p.Hkv * p.row_blocks * p.num_splits;
-  const int grid = (int)std::min<int64_t>(items, device_sms());
+  const int grid = p.balanced ? device_sms() : (int)std::min<int64_t>(items, device_sms());
   prefill_kernel<BWK, BWV><<<grid, kThreads, M::kDynamic, stream>>>(p);
   note_launches(1);
   return check_cuda(cudaGetLastError(), "wtq_prefill launch");
@@ -581,21 +691,24 @@ int chunk_tokens_for(int max_tokens, int splits) {
   return tokens < 256 ? 256 : tokens;
 }
 
-}  // namespace pf
-}  // namespace wtq
-
-using namespace wtq;
-
-extern "C" int wtq_prefill_auto_splits(int B, int Hq, int Hkv, int Q, int max_pages, int S) {
-  if (B < 1 || Hq < 1 || Hkv < 1 || Q < 1 || max_pages < 1 || S < 1 || Hq % Hkv) return 1;
-  const int64_t max_tokens = (int64_t)max_pages * S;
-  const int row_blocks = (Q * (Hq / Hkv) + pf::kRows - 1) / pf::kRows;
+// Shapes the balanced schedule serves: enough query rows for the tensor-core merge, at
+// least half as many groups as multiprocessors (a run is never shorter than half a
+// group, so fewer groups would leave blocks idle), and a plan that fits.
+bool balanced_shape(int B, int Hq, int Hkv, int Q) {
+  const int row_blocks = (Q * (Hq / Hkv) + kRows - 1) / kRows;
   const int64_t groups = (int64_t)B * Hkv * row_blocks;
-  // Items = groups x chunks run in waves of one per multiprocessor; every chunk beyond the
-  // first adds about 5 % (states to write and merge, queries to reload).  Both effects were
-  // measured at 16 x 8 kv heads x 8k tokens: 64 query tokens (128 groups) 690 / 726 / 769 us
-  // with 1 / 2 / 3 chunks, 256 query tokens (512 groups) 2549 / 2388 / 2633 us.  Take the
-  // count with the lowest modelled cost; chunks of at least 256 tokens.
+  return (int64_t)B * Q * Hq >= 4096 && 2 * groups >= device_sms() &&
+         (int64_t)B * row_blocks <= kMaxPairs;
+}
+
+// Equal chunks: items = groups x chunks run in waves of one per multiprocessor; every chunk
+// beyond the first adds about 5 % (states to write and merge, queries to reload).  Both
+// effects were measured at 16 x 8 kv heads x 8k tokens: 64 query tokens (128 groups) 690 /
+// 726 / 769 us with 1 / 2 / 3 chunks, 256 query tokens (512 groups) 2549 / 2388 / 2633 us.
+// Takes the count with the lowest modelled cost; chunks of at least 256 tokens.
+int equal_chunks(int B, int Hq, int Hkv, int Q, int64_t max_tokens) {
+  const int row_blocks = (Q * (Hq / Hkv) + kRows - 1) / kRows;
+  const int64_t groups = (int64_t)B * Hkv * row_blocks;
   const int64_t sms = device_sms();
   const int64_t most = std::max<int64_t>(1, std::min<int64_t>(max_tokens / 256, 32));
   int64_t splits = 1;
@@ -609,9 +722,23 @@ extern "C" int wtq_prefill_auto_splits(int B, int Hq, int Hkv, int Q, int max_pa
     }
   }
   // chunk sizes round up to whole tiles: drop chunks that would stay empty
-  const int tokens = pf::chunk_tokens_for((int)max_tokens, (int)splits);
+  const int tokens = chunk_tokens_for((int)max_tokens, (int)splits);
   return (int)((max_tokens + tokens - 1) / tokens);
 }
+
+}  // namespace pf
+}  // namespace wtq
+
+using namespace wtq;
+
+extern "C" int wtq_prefill_auto_splits(int B, int Hq, int Hkv, int Q, int max_pages, int S) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Q < 1 || max_pages < 1 || S < 1 || Hq % Hkv) return 1;
+  if (pf::balanced_shape(B, Hq, Hkv, Q)) return pf::kBalancedSlots;
+  return pf::equal_chunks(B, Hq, Hkv, Q, (int64_t)max_pages * S);
+}
+
+static thread_local int g_last_schedule = -1;
+extern "C" int wtq_prefill_last_schedule(void) { return g_last_schedule; }
 
 extern "C" size_t wtq_prefill_workspace_bytes(int B, int Hq, int Hkv, int Q, int D, int num_splits) {
   if (B < 1 || Hq < 1 || Hkv < 1 || Q < 1 || D < 1 || num_splits < 1) return 0;
@@ -640,11 +767,29 @@ extern "C" int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2],
   if (B == 0) return WTQ_OK;
   if (!workspace) return fail(WTQ_ERR_ARG, "wtq_prefill: null workspace");
   const int max_tokens = max_pages * S;
-  int splits = num_splits > 0 ? num_splits : wtq_prefill_auto_splits(B, Hq, Hkv, Q, max_pages, S);
+  const int64_t total_rows = (int64_t)B * Q * Hq;
+  // Schedule.  An explicit num_splits cuts every history into that many equal chunks.
+  // Left to the library (num_splits <= 0), shapes with enough groups and rows take the
+  // balanced schedule (tiles dealt evenly to the blocks, three chunk slots per row) when
+  // the output layout lets the tensor-core merge run; everything else takes equal chunks,
+  // never more than wtq_prefill_auto_splits promised the caller's workspace.
+  bool balanced = false;
+  int splits = num_splits;
+  if (num_splits <= 0) {
+    splits = pf::equal_chunks(B, Hq, Hkv, Q, max_tokens);
+    if (Hq % Hkv == 0 && pf::balanced_shape(B, Hq, Hkv, Q)) {
+      MergeParams fit = {};
+      fit.D = D; fit.Hq = Hq; fit.num_splits = pf::kBalancedSlots; fit.out = out;
+      fit.osb = out_strides[0]; fit.osh = out_strides[1]; fit.Pi_v = v_side->Pi;
+      fit.part_acc = (float *)workspace;                 // states start at a multiple of 256 bytes from here
+      balanced = rows_mma_merge_eligible(fit, total_rows);
+      splits = std::min(splits, pf::kBalancedSlots);
+    }
+  }
   splits = std::min(splits, std::max(1, max_tokens / pf::kTile));
   splits = std::min(splits, 256);
   const int chunk_tokens = pf::chunk_tokens_for(max_tokens, splits);
-  splits = (max_tokens + chunk_tokens - 1) / chunk_tokens;
+  splits = balanced ? pf::kBalancedSlots : (max_tokens + chunk_tokens - 1) / chunk_tokens;
   const size_t need = wtq_prefill_workspace_bytes(B, Hq, Hkv, Q, D, splits);
   if (workspace_bytes < need)
     return fail(WTQ_ERR_WORKSPACE, "wtq_prefill: workspace %zu < %zu bytes", workspace_bytes, need);
@@ -678,6 +823,8 @@ extern "C" int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2],
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.n_rep = Hq / Hkv; p.Q = Q; p.S = S; p.P = P;
   p.max_pages = max_pages; p.max_tokens = max_tokens; p.num_splits = splits;
   p.chunk_tokens = chunk_tokens;
+  p.balanced = balanced ? 1 : 0;
+  g_last_schedule = p.balanced;
   p.row_blocks = (Q * p.n_rep + pf::kRows - 1) / pf::kRows;
   p.status = status;
   if ((int64_t)B * Hkv * p.row_blocks * splits > (int64_t)1 << 30)
@@ -693,11 +840,13 @@ extern "C" int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2],
                 "aligned pages");
   if (cudaMemsetAsync(p.work_counter, 0, 256, stream) != cudaSuccess)
     return check_cuda(cudaGetLastError(), "wtq_prefill: counter reset");
+  // balanced schedule: a row's slots that no piece writes must read as empty (l = 0)
+  if (balanced && cudaMemsetAsync(p.part_l, 0, rows * splits * sizeof(float), stream) != cudaSuccess)
+    return check_cuda(cudaGetLastError(), "wtq_prefill: chunk state reset");
   // rotation of the B * Q * Hq query rows (exp2 domain) and the lookup tables
   ScanSetup setup = {nullptr, (uint32_t *)p.lut, k_side->centroids, v_side->centroids, k_side->bw,
                      v_side->bw, mma_lut_words(k_side->bw, v_side->bw)};
   const float q_scale = scale * 1.4426950408889634f;
-  const int64_t total_rows = (int64_t)B * Q * Hq;
   if (rows_mma_rotate_eligible(q, q_strides[0], q_strides[1], Hq, D, total_rows, k_side->Pi, q_rot)) {
     if (int rc = launch_rotate_rows_mma(q, dtype, k_side->Pi, q_scale, total_rows, q_rot, setup, status,
                                         stream))
@@ -717,7 +866,10 @@ extern "C" int wtq_prefill(const void *q, int dtype, const int64_t q_strides[2],
   m.Pi_v = v_side->Pi; m.out = out; m.osb = out_strides[0]; m.osh = out_strides[1];
   m.dtype = dtype; m.Hq = Hq; m.D = D; m.num_splits = splits;
   m.work_counter = nullptr;
-  if (rows_mma_merge_eligible(m, total_rows))
-    return launch_merge_rows_mma(m, p.row_lens, total_rows, chunk_tokens, max_tokens, status, stream);
+  // (balanced: slot c of a row is read when the row sees more than c tokens; a piece in
+  // slot c starts at tile c or later, so no filled slot goes unread)
+  if (balanced || rows_mma_merge_eligible(m, total_rows))
+    return launch_merge_rows_mma(m, p.row_lens, total_rows, balanced ? 1 : chunk_tokens, max_tokens, status,
+                                 stream);
   return launch_mma_merge(m, p.row_lens, B * Q, Hkv, p.n_rep, chunk_tokens, max_tokens, stream);
 }

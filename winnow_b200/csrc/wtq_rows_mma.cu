@@ -144,8 +144,10 @@ __global__ void __launch_bounds__(kThreads, 1) rows_kernel(Params p) {
       float mv[kMaxChunks], lv[kMaxChunks], gmax = -INFINITY, denom = 0.f;
 #pragma unroll
       for (int c = 0; c < kMaxChunks; ++c) {
-        mv[c] = c < chunks ? __ldcg(p.part_m + row * p.num_splits + c) : -INFINITY;
+        // a state with l = 0 is empty (nothing seen, or never written): its m and
+        // accumulator are not read
         lv[c] = c < chunks ? __ldcg(p.part_l + row * p.num_splits + c) : 0.f;
+        mv[c] = lv[c] > 0.f ? __ldcg(p.part_m + row * p.num_splits + c) : -INFINITY;
         gmax = fmaxf(gmax, mv[c]);
       }
 #pragma unroll
@@ -183,9 +185,11 @@ __global__ void __launch_bounds__(kThreads, 1) rows_kernel(Params p) {
         for (int c = 0; c < kMaxChunks; ++c) {
           if (c < chunks_of[m][h]) {
             const float w = __uint_as_float(lds32(weights + (uint32_t)(lr * kMaxChunks + c) * 4u));
-            const float2 v = __ldcg(reinterpret_cast<const float2 *>(src + c * 128));
-            a.x = fmaf(w, v.x, a.x);
-            a.y = fmaf(w, v.y, a.y);
+            if (w != 0.f) {
+              const float2 v = __ldcg(reinterpret_cast<const float2 *>(src + c * 128));
+              a.x = fmaf(w, v.x, a.x);
+              a.y = fmaf(w, v.y, a.y);
+            }
           }
         }
         return a;

@@ -214,7 +214,8 @@ def packed_prefill_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
         return out.zero_().permute(0, 2, 1, 3)
     rows = q.permute(0, 2, 1, 3).contiguous()                 # (B, Q, Hq, D): row b * Q + i
     L = _lib.lib()
-    splits = int(num_splits or 0) or L.wtq_prefill_auto_splits(B, Hq, Hkv, Q, max_pages, S)
+    asked = max(int(num_splits or 0), 0)                      # 0: the library chooses the schedule
+    splits = asked or L.wtq_prefill_auto_splits(B, Hq, Hkv, Q, max_pages, S)
     need = L.wtq_prefill_workspace_bytes(B, Hq, Hkv, Q, D, splits)
     if workspace is None:
         key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
@@ -228,7 +229,7 @@ def packed_prefill_attention(q: torch.Tensor, kv: pa.PackedKV, scale: float, *,
             rows.data_ptr(), _lib.dtype_code(q.dtype), _lib.i64x(Hq * D, D), out.data_ptr(),
             _lib.i64x(Hq * D, D), ctypes.byref(k_side), ctypes.byref(v_side),
             kv.page_table.data_ptr(), kv.page_table.stride(0), kv.seq_lens.data_ptr(), float(scale),
-            B, Hq, Hkv, Q, D, S, P, max_pages, splits, workspace.data_ptr(), workspace.numel(),
+            B, Hq, Hkv, Q, D, S, P, max_pages, asked, workspace.data_ptr(), workspace.numel(),
             status.data_ptr() if status is not None else None,
             torch.cuda.current_stream(dev).cuda_stream))
     return out.permute(0, 2, 1, 3)
